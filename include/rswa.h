@@ -1,0 +1,173 @@
+/* rswa.h -- C ABI of the B200 (sm_100a) ring sliding-window attention kernels.
+ *
+ * Plain pointers and sizes only.  Every buffer, workspace included, is owned by the caller;
+ * all work is enqueued on the stream passed in; nothing here allocates device memory (except
+ * where an entry point says otherwise) and nothing synchronises the device.  Entry points
+ * return 0 on success and a negative RSWA_E_* code on a rejected argument; rswa_last_error()
+ * gives the message for the calling thread.
+ *
+ * What each entry point replaces in the reference (paths are inside the reference project):
+ * the reference reaches its arithmetic through four Python wrappers around the flash-attn
+ * custom ops and one Triton merge kernel; the entry points below are what a maintainer binds
+ * instead (with ctypes).
+ */
+#ifndef RSWA_H_
+#define RSWA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RSWA_ABI_VERSION 1
+#define RSWA_MAX_SPANS 10
+#define RSWA_TILE 128 /* query rows and key rows per tile */
+
+#define RSWA_DTYPE_BF16 0
+#define RSWA_DTYPE_FP16 1
+
+#define RSWA_OK 0
+#define RSWA_E_ARG (-1)      /* bad shape / stride / alignment / null pointer */
+#define RSWA_E_UNSUPPORTED (-2)
+#define RSWA_E_CUDA (-3)     /* a CUDA runtime/driver call failed at launch time */
+#define RSWA_E_NOALLOC_SIZE (-4)
+
+/* bits of rswa_bwd_params_t.flags */
+#define RSWA_BWD_INIT 1   /* compute delta = rowsum(dO*O) and zero the fp32 dQ accumulator */
+#define RSWA_BWD_FINISH 2 /* scale + convert the fp32 dQ accumulator into dq */
+
+/* A span is a run of consecutive tokens' K and V (and, in backward, their gradients) that sits
+ * in one buffer: the rank's own tokens, a halo received from an earlier rank, or the sink
+ * tokens received from the owner of the sequence start.  Spans of one call must not overlap in
+ * position.  Layout [batch, len, n_kv_heads, head_dim], strides in elements, head_dim
+ * contiguous. */
+typedef struct rswa_span {
+  const void* k;
+  const void* v;
+  void* dk; /* backward only; bf16/fp16 like k, or float when grad_fp32 != 0 */
+  void* dv;
+  int64_t kv_stride_b, kv_stride_t, kv_stride_h;     /* k and v share strides */
+  int64_t dkv_stride_b, dkv_stride_t, dkv_stride_h;  /* dk and dv share strides */
+  int32_t pos_start; /* global position of the span's first token */
+  int32_t len;       /* tokens */
+  int32_t grad_fp32;
+  int32_t reserved;
+} rswa_span_t;
+
+/* Shared geometry.  A query at global position p sees key t iff both lie in the same sequence,
+ * t <= p, and (p - t <= window  or  t < seq_start(p) + n_sink).  Sequences are the batch rows
+ * when cu_seqlens is NULL, else the segments of the packed token axis given by the GLOBAL
+ * cumulative lengths (int32, device memory, n_seqs + 1 entries) and batch must be 1. */
+typedef struct rswa_geom {
+  int32_t dtype;
+  int32_t batch, q_len, n_q_heads, n_kv_heads, head_dim; /* head_dim must be 128 */
+  int32_t q_pos_start; /* global position of local query 0 */
+  int32_t window, n_sink;
+  float softmax_scale;
+  const int32_t* cu_seqlens;
+  int32_t n_seqs;
+  int32_t n_spans;
+  rswa_span_t spans[RSWA_MAX_SPANS];
+} rswa_geom_t;
+
+/* Forward: out [batch,q_len,Hq,D] and lse [batch,Hq,q_len] (natural log, fp32; -inf and a zero
+ * output row where no key of the given spans is visible).  Only query tiles
+ * [q_tile_begin, q_tile_end) are computed (q_tile_end <= 0: all).
+ * Replaces wrapped_flash_attn_fwd / wrapped_flash_attn_fwd_varlen
+ * (ring_swa/ops/wrap_flash.py:168-200, 203-273) and the per-hop mask-case selection around them
+ * (ring_swa/sliding_window/nonvarlen.py:95-150, ring_swa/ops/attn.py:12-60). */
+typedef struct rswa_fwd_params {
+  rswa_geom_t g;
+  const void* q;
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  void* out;
+  int64_t o_stride_b, o_stride_t, o_stride_h;
+  float* lse;
+  int64_t lse_stride_b, lse_stride_h;
+  int32_t q_tile_begin, q_tile_end;
+  int32_t* status; /* device word; set non-zero if a device-side wait ran out */
+} rswa_fwd_params_t;
+
+int rswa_fwd(const rswa_fwd_params_t* p, void* stream);
+
+/* Backward: dq [batch,q_len,Hq,D] and per-span dk/dv from (dO, q, spans, out, lse), using the
+ * final (merged) out and lse.  `workspace` is rswa_bwd_workspace_bytes() of device memory: the
+ * fp32 dQ accumulator and the fp32 delta rows.  One call with flags INIT|FINISH does a whole
+ * backward; a ring rank calls it once per group of spans (INIT on the first, FINISH on the last)
+ * with the same workspace so that dQ accumulates across them.
+ * Replaces wrapped_flash_attn_bwd / wrapped_flash_attn_bwd_varlen
+ * (ring_swa/ops/wrap_flash.py:276-327, 330-429) and ring_swa/ops/attn.py:63-126. */
+typedef struct rswa_bwd_params {
+  rswa_geom_t g;
+  const void* q;
+  int64_t q_stride_b, q_stride_t, q_stride_h;
+  const void* out;
+  int64_t o_stride_b, o_stride_t, o_stride_h;
+  const void* dout;
+  int64_t do_stride_b, do_stride_t, do_stride_h;
+  const float* lse;
+  int64_t lse_stride_b, lse_stride_h;
+  void* dq;
+  int64_t dq_stride_b, dq_stride_t, dq_stride_h;
+  void* workspace;
+  int64_t workspace_bytes;
+  int32_t flags;
+  int32_t* status;
+} rswa_bwd_params_t;
+
+int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_t n_q_heads, int32_t head_dim);
+int rswa_bwd(const rswa_bwd_params_t* p, void* stream);
+
+/* Log-sum-exp merge of two partial results over the same queries:
+ *   lse = log(exp(lse_a) + exp(lse_b)),  o = o_a*exp(lse_a-lse) + o_b*exp(lse_b-lse)
+ * o_* are [rows, D] 16-bit with a row stride (rows = batch*q_len*Hq flattened by the caller's
+ * strides below), lse_* fp32.  In place (o == o_a, lse == lse_a) is allowed.  (-inf,-inf) gives
+ * (0,-inf).  Replaces merge_attn_out (ring_swa/ops/merge.py:150-193, kernel :68-147). */
+typedef struct rswa_merge_params {
+  int32_t dtype;
+  int32_t batch, q_len, n_heads, head_dim;
+  const void* o_a;
+  const void* o_b;
+  void* o;
+  int64_t oa_stride_b, oa_stride_t, oa_stride_h;
+  int64_t ob_stride_b, ob_stride_t, ob_stride_h;
+  int64_t o_stride_b, o_stride_t, o_stride_h;
+  const float* lse_a;
+  const float* lse_b;
+  float* lse; /* all three [batch, n_heads, q_len] with the strides below */
+  int64_t lse_stride_b, lse_stride_h;
+} rswa_merge_params_t;
+
+int rswa_merge(const rswa_merge_params_t* p, void* stream);
+
+/* acc[b, t, :] += recv[b, t, :] for a [batch, len, row] block: adds the K/V gradients a later
+ * rank computed for this rank's trailing tokens (the halo) into the fp32 accumulator.
+ * recv_dtype: RSWA_DTYPE_* or 2 for float.  Replaces the dkv.add_ of the reverse ring
+ * (ring_swa/sliding_window/nonvarlen.py:313-322). */
+int rswa_halo_accumulate(float* acc, int64_t acc_stride_b, const void* recv, int64_t recv_stride_b,
+                         int32_t recv_dtype, int32_t batch, int64_t elems_per_batch, void* stream);
+
+/* dst (16-bit) = src (float), [batch, elems_per_batch] with batch strides: the final cast of
+ * ring_swa/sliding_window/nonvarlen.py:335-337. */
+int rswa_cast_from_f32(void* dst, int64_t dst_stride_b, const float* src, int64_t src_stride_b,
+                       int32_t dtype, int32_t batch, int64_t elems_per_batch, void* stream);
+
+/* One 128x128x128 tensor-core product through each operand path the attention kernels use
+ * (shared-memory K-major / MN-major operands, tensor-memory A operand); for the unit tests.
+ * a, b: bf16 [128,128] row-major device buffers; d: float [128,128].
+ *   mode 0: d = a * b^T      (both K-major)
+ *   mode 1: d = a * b        (B MN-major)
+ *   mode 2: d = a * b        (A through tensor memory, B MN-major)
+ *   mode 3: d = a^T * b      (A and B MN-major)
+ * No counterpart in the reference. */
+int rswa_selftest_mma(int32_t mode, const void* a, const void* b, float* d, int32_t* status,
+                      void* stream);
+
+int rswa_abi_version(void);
+const char* rswa_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RSWA_H_ */

@@ -1,0 +1,318 @@
+// C-ABI layer: argument checks, TMA descriptor set-up, launches.  See include/rswa.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "rswa_common.cuh"
+
+namespace rswa {
+
+int launch_fwd(const FwdKernelParams& kp, int dtype, cudaStream_t stream);
+int launch_bwd(const BwdKernelParams& kp, int dtype, int total_key_tiles, cudaStream_t stream);
+int launch_delta(const rswa_bwd_params_t& p, float* delta, int q_len_pad, cudaStream_t stream);
+int launch_dq_convert(const rswa_bwd_params_t& p, const float* dq_acc, cudaStream_t stream);
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || sym == nullptr) {
+    set_error("cuTensorMapEncodeTiled not available: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+
+int make_tile_map(CUtensorMap* map, const void* base, int dtype, int batch, int tokens, int heads,
+                  long long sb, long long st, long long sh) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return RSWA_E_CUDA;
+  if (base == nullptr || (reinterpret_cast<uintptr_t>(base) & 15) != 0) {
+    set_error("tensor base pointer must be non-null and 16-byte aligned");
+    return RSWA_E_ARG;
+  }
+  if (tokens <= 0 || heads <= 0 || batch <= 0) {
+    set_error("tensor extents must be positive (batch %d, tokens %d, heads %d)", batch, tokens, heads);
+    return RSWA_E_ARG;
+  }
+  if ((sb % 8) != 0 || (st % 8) != 0 || (sh % 8) != 0 || st <= 0 || sh <= 0 || sb < 0) {
+    set_error("tensor strides must be positive multiples of 8 elements (got %lld, %lld, %lld)", sb, st, sh);
+    return RSWA_E_ARG;
+  }
+  if (batch == 1 && sb == 0) sb = static_cast<long long>(tokens) * st;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(heads),
+                        static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(sh) * 2, static_cast<cuuint64_t>(st) * 2,
+                           static_cast<cuuint64_t>(sb) * 2};
+  cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(kTile), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, dtype == RSWA_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                   4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with code %d (tokens %d heads %d strides %lld %lld %lld)",
+              static_cast<int>(r), tokens, heads, sb, st, sh);
+    return RSWA_E_CUDA;
+  }
+  return RSWA_OK;
+}
+
+int check_geom(const rswa_geom_t& g, bool need_grads) {
+  if (g.dtype != RSWA_DTYPE_BF16 && g.dtype != RSWA_DTYPE_FP16) {
+    set_error("dtype must be bf16 (0) or fp16 (1), got %d", g.dtype);
+    return RSWA_E_UNSUPPORTED;
+  }
+  if (g.head_dim != kHeadDim) {
+    set_error("head_dim must be %d, got %d", kHeadDim, g.head_dim);
+    return RSWA_E_UNSUPPORTED;
+  }
+  if (g.batch <= 0 || g.q_len <= 0 || g.n_q_heads <= 0 || g.n_kv_heads <= 0) {
+    set_error("batch, q_len and head counts must be positive");
+    return RSWA_E_ARG;
+  }
+  if (g.n_q_heads % g.n_kv_heads != 0) {
+    set_error("Number of query heads must be divisible by number of key/value heads");
+    return RSWA_E_ARG;
+  }
+  if (g.window < 0 || g.n_sink < 0 || g.q_pos_start < 0) {
+    set_error("window, n_sink and q_pos_start must be non-negative");
+    return RSWA_E_ARG;
+  }
+  if (!(g.softmax_scale > 0.f)) {
+    set_error("softmax_scale must be positive");
+    return RSWA_E_ARG;
+  }
+  if (g.cu_seqlens != nullptr && (g.batch != 1 || g.n_seqs <= 0)) {
+    set_error("packed (cu_seqlens) input needs batch == 1 and n_seqs > 0");
+    return RSWA_E_ARG;
+  }
+  if (g.n_spans < 0 || g.n_spans > RSWA_MAX_SPANS) {
+    set_error("n_spans must be in [0, %d]", RSWA_MAX_SPANS);
+    return RSWA_E_ARG;
+  }
+  if (static_cast<long long>(g.q_pos_start) + g.q_len + g.window >= 0x7fffffffLL) {
+    set_error("positions overflow int32");
+    return RSWA_E_ARG;
+  }
+  for (int i = 0; i < g.n_spans; ++i) {
+    const rswa_span_t& s = g.spans[i];
+    if (s.len <= 0 || s.pos_start < 0 || s.k == nullptr || s.v == nullptr) {
+      set_error("span %d: needs k, v, len > 0 and pos_start >= 0", i);
+      return RSWA_E_ARG;
+    }
+    if (need_grads && (s.dk == nullptr || s.dv == nullptr)) {
+      set_error("span %d: dk and dv are required in backward", i);
+      return RSWA_E_ARG;
+    }
+    for (int j = 0; j < i; ++j) {
+      const rswa_span_t& o = g.spans[j];
+      if (s.pos_start < o.pos_start + o.len && o.pos_start < s.pos_start + s.len) {
+        set_error("spans %d and %d overlap in position", j, i);
+        return RSWA_E_ARG;
+      }
+    }
+  }
+  return RSWA_OK;
+}
+
+static int fill_span_maps(const rswa_geom_t& g, CUtensorMap* kmaps, CUtensorMap* vmaps, int* pos, int* len) {
+  for (int i = 0; i < g.n_spans; ++i) {
+    const rswa_span_t& s = g.spans[i];
+    int rc = make_tile_map(&kmaps[i], s.k, g.dtype, g.batch, s.len, g.n_kv_heads, s.kv_stride_b, s.kv_stride_t,
+                           s.kv_stride_h);
+    if (rc) return rc;
+    rc = make_tile_map(&vmaps[i], s.v, g.dtype, g.batch, s.len, g.n_kv_heads, s.kv_stride_b, s.kv_stride_t,
+                       s.kv_stride_h);
+    if (rc) return rc;
+    pos[i] = s.pos_start;
+    len[i] = s.len;
+  }
+  return RSWA_OK;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace rswa
+
+using namespace rswa;
+
+extern "C" int rswa_abi_version(void) { return RSWA_ABI_VERSION; }
+extern "C" const char* rswa_last_error(void) { return g_err; }
+
+extern "C" int rswa_fwd(const rswa_fwd_params_t* p, void* stream) {
+  if (p == nullptr) {
+    set_error("rswa_fwd: null params");
+    return RSWA_E_ARG;
+  }
+  const rswa_geom_t& g = p->g;
+  int rc = check_geom(g, false);
+  if (rc) return rc;
+  if (p->q == nullptr || p->out == nullptr || p->lse == nullptr || p->status == nullptr) {
+    set_error("rswa_fwd: q, out, lse and status are required");
+    return RSWA_E_ARG;
+  }
+  if (!aligned16(p->out) || (p->o_stride_b % 8) || (p->o_stride_t % 8) || (p->o_stride_h % 8)) {
+    set_error("rswa_fwd: out must be 16-byte aligned with strides that are multiples of 8 elements");
+    return RSWA_E_ARG;
+  }
+  const int n_tiles_all = (g.q_len + kTile - 1) / kTile;
+  int qb = p->q_tile_begin, qe = p->q_tile_end <= 0 ? n_tiles_all : p->q_tile_end;
+  if (qb < 0 || qe > n_tiles_all || qb > qe) {
+    set_error("rswa_fwd: query tile range [%d, %d) outside [0, %d]", qb, qe, n_tiles_all);
+    return RSWA_E_ARG;
+  }
+  FwdKernelParams kp;
+  memset(&kp, 0, sizeof(kp));
+  rc = make_tile_map(&kp.q_map, p->q, g.dtype, g.batch, g.q_len, g.n_q_heads, p->q_stride_b, p->q_stride_t,
+                     p->q_stride_h);
+  if (rc) return rc;
+  rc = fill_span_maps(g, kp.k_map, kp.v_map, kp.span_pos, kp.span_len);
+  if (rc) return rc;
+  kp.n_spans = g.n_spans;
+  kp.batch = g.batch;
+  kp.q_len = g.q_len;
+  kp.hq = g.n_q_heads;
+  kp.hkv = g.n_kv_heads;
+  kp.q_pos_start = g.q_pos_start;
+  kp.window = g.window;
+  kp.n_sink = g.n_sink;
+  kp.scale_log2 = g.softmax_scale * 1.4426950408889634f;
+  kp.cu = g.cu_seqlens;
+  kp.n_seqs = g.n_seqs;
+  kp.out = p->out;
+  kp.o_sb = p->o_stride_b;
+  kp.o_st = p->o_stride_t;
+  kp.o_sh = p->o_stride_h;
+  kp.lse = p->lse;
+  kp.l_sb = p->lse_stride_b;
+  kp.l_sh = p->lse_stride_h;
+  kp.q_tile_begin = qb;
+  kp.n_q_tiles = qe - qb;
+  kp.status = p->status;
+  return launch_fwd(kp, g.dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_t n_q_heads, int32_t head_dim) {
+  if (batch <= 0 || q_len <= 0 || n_q_heads <= 0 || head_dim != kHeadDim) return -1;
+  const int64_t q_len_pad = (static_cast<int64_t>(q_len) + kTile - 1) / kTile * kTile;
+  const int64_t dq = static_cast<int64_t>(batch) * q_len * n_q_heads * head_dim * 4;
+  const int64_t delta = static_cast<int64_t>(batch) * n_q_heads * q_len_pad * 4;
+  return ((dq + 255) / 256) * 256 + delta;
+}
+
+extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
+  if (p == nullptr) {
+    set_error("rswa_bwd: null params");
+    return RSWA_E_ARG;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const rswa_geom_t& g = p->g;
+  int rc = check_geom(g, true);
+  if (rc) return rc;
+  if (!p->q || !p->out || !p->dout || !p->lse || !p->dq || !p->workspace || !p->status) {
+    set_error("rswa_bwd: q, out, dout, lse, dq, workspace and status are required");
+    return RSWA_E_ARG;
+  }
+  const int64_t need = rswa_bwd_workspace_bytes(g.batch, g.q_len, g.n_q_heads, g.head_dim);
+  if (p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255) != 0) {
+    set_error("rswa_bwd: workspace needs %lld bytes, 256-byte aligned (got %lld)", (long long)need,
+              (long long)p->workspace_bytes);
+    return RSWA_E_ARG;
+  }
+  if (!aligned16(p->dq) || (p->dq_stride_b % 8) || (p->dq_stride_t % 8) || (p->dq_stride_h % 8) ||
+      !aligned16(p->out) || (p->o_stride_t % 8) || (p->o_stride_h % 8) || (p->o_stride_b % 8)) {
+    set_error("rswa_bwd: dq/out must be 16-byte aligned with strides that are multiples of 8 elements");
+    return RSWA_E_ARG;
+  }
+  const int q_len_pad = (g.q_len + kTile - 1) / kTile * kTile;
+  const int64_t dq_bytes = static_cast<int64_t>(g.batch) * g.q_len * g.n_q_heads * kHeadDim * 4;
+  float* dq_acc = static_cast<float*>(p->workspace);
+  float* delta = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + ((dq_bytes + 255) / 256) * 256);
+
+  BwdKernelParams kp;
+  memset(&kp, 0, sizeof(kp));
+  rc = make_tile_map(&kp.q_map, p->q, g.dtype, g.batch, g.q_len, g.n_q_heads, p->q_stride_b, p->q_stride_t,
+                     p->q_stride_h);
+  if (rc) return rc;
+  rc = make_tile_map(&kp.do_map, p->dout, g.dtype, g.batch, g.q_len, g.n_q_heads, p->do_stride_b,
+                     p->do_stride_t, p->do_stride_h);
+  if (rc) return rc;
+  rc = fill_span_maps(g, kp.k_map, kp.v_map, kp.span_pos, kp.span_len);
+  if (rc) return rc;
+  int total_tiles = 0;
+  for (int i = 0; i < g.n_spans; ++i) {
+    const rswa_span_t& s = g.spans[i];
+    kp.span_tile0[i] = total_tiles;
+    total_tiles += (s.len + kTile - 1) / kTile;
+    kp.dk[i] = s.dk;
+    kp.dv[i] = s.dv;
+    kp.dkv_sb[i] = s.dkv_stride_b;
+    kp.dkv_st[i] = s.dkv_stride_t;
+    kp.dkv_sh[i] = s.dkv_stride_h;
+    kp.grad_fp32[i] = s.grad_fp32;
+    const int al = s.grad_fp32 ? 4 : 8;
+    if (!aligned16(s.dk) || !aligned16(s.dv) || (s.dkv_stride_b % al) || (s.dkv_stride_t % al) ||
+        (s.dkv_stride_h % al)) {
+      set_error("rswa_bwd: span %d dk/dv must be 16-byte aligned with 16-byte multiple strides", i);
+      return RSWA_E_ARG;
+    }
+  }
+  kp.span_tile0[g.n_spans] = total_tiles;
+  kp.n_spans = g.n_spans;
+  kp.batch = g.batch;
+  kp.q_len = g.q_len;
+  kp.hq = g.n_q_heads;
+  kp.hkv = g.n_kv_heads;
+  kp.q_pos_start = g.q_pos_start;
+  kp.window = g.window;
+  kp.n_sink = g.n_sink;
+  kp.scale = g.softmax_scale;
+  kp.scale_log2 = g.softmax_scale * 1.4426950408889634f;
+  kp.cu = g.cu_seqlens;
+  kp.n_seqs = g.n_seqs;
+  kp.lse = p->lse;
+  kp.l_sb = p->lse_stride_b;
+  kp.l_sh = p->lse_stride_h;
+  kp.delta = delta;
+  kp.d_sb = static_cast<long long>(g.n_q_heads) * q_len_pad;
+  kp.d_sh = q_len_pad;
+  kp.dq_acc = dq_acc;
+  kp.status = p->status;
+
+  if (p->flags & RSWA_BWD_INIT) {
+    cudaError_t e = cudaMemsetAsync(dq_acc, 0, dq_bytes, stream);
+    if (e != cudaSuccess) {
+      set_error("rswa_bwd: memset: %s", cudaGetErrorString(e));
+      return RSWA_E_CUDA;
+    }
+    rc = launch_delta(*p, delta, q_len_pad, stream);
+    if (rc) return rc;
+  }
+  if (total_tiles > 0) {
+    rc = launch_bwd(kp, g.dtype, total_tiles, stream);
+    if (rc) return rc;
+  }
+  if (p->flags & RSWA_BWD_FINISH) {
+    rc = launch_dq_convert(*p, dq_acc, stream);
+    if (rc) return rc;
+  }
+  return RSWA_OK;
+}

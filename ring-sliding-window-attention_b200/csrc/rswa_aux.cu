@@ -1,0 +1,261 @@
+// Bandwidth-bound helpers around the attention kernels: delta = rowsum(dO * O), fp32 dQ -> 16-bit,
+// the log-sum-exp merge of two partial results, halo-gradient accumulation and the final cast.
+// All are straight streaming kernels: 16-byte accesses, one warp per 128-element row where rows
+// are involved, grid sized from the data.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "rswa_common.cuh"
+
+namespace rswa {
+namespace {
+
+template <bool kBf16>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if constexpr (kBf16) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  } else {
+    __half2 h = *reinterpret_cast<__half2*>(&w);
+    return __half22float2(h);
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2f(float lo, float hi) {
+  if constexpr (kBf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+// One warp per (b, t, h) row of 128 elements: lane handles 4 consecutive elements (8 bytes).
+template <bool kBf16>
+__global__ void delta_kernel(const uint16_t* __restrict__ out, long long o_sb, long long o_st, long long o_sh,
+                             const uint16_t* __restrict__ dout, long long d_sb, long long d_st, long long d_sh,
+                             float* __restrict__ delta, int batch, int q_len, int hq, int q_len_pad) {
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long n_rows = static_cast<long long>(batch) * q_len * hq;
+  if (row >= n_rows) return;
+  const int h = row % hq;
+  const long long bt = row / hq;
+  const int t = bt % q_len;
+  const int b = bt / q_len;
+  const uint2 a = *reinterpret_cast<const uint2*>(out + b * o_sb + t * o_st + h * o_sh + lane * 4);
+  const uint2 d = *reinterpret_cast<const uint2*>(dout + b * d_sb + t * d_st + h * d_sh + lane * 4);
+  const float2 a0 = unpack2<kBf16>(a.x), a1 = unpack2<kBf16>(a.y);
+  const float2 d0 = unpack2<kBf16>(d.x), d1 = unpack2<kBf16>(d.y);
+  float s = a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) delta[(static_cast<long long>(b) * hq + h) * q_len_pad + t] = s;
+}
+
+// dq = scale * dq_acc, fp32 [b, t, h, 128] contiguous -> 16-bit with strides.  8 elements/thread.
+template <bool kBf16>
+__global__ void dq_convert_kernel(const float* __restrict__ acc, uint16_t* __restrict__ dq, long long sb,
+                                  long long st, long long sh, int q_len, int hq, long long n_vec, float scale) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const int c = i & 15;  // 16 vectors of 8 per 128-element row
+  const long long row = i >> 4;
+  const int h = row % hq;
+  const long long bt = row / hq;
+  const int t = bt % q_len;
+  const long long b = bt / q_len;
+  const float4 x = reinterpret_cast<const float4*>(acc)[i * 2];
+  const float4 y = reinterpret_cast<const float4*>(acc)[i * 2 + 1];
+  uint4 o;
+  o.x = pack2f<kBf16>(x.x * scale, x.y * scale);
+  o.y = pack2f<kBf16>(x.z * scale, x.w * scale);
+  o.z = pack2f<kBf16>(y.x * scale, y.y * scale);
+  o.w = pack2f<kBf16>(y.z * scale, y.w * scale);
+  *reinterpret_cast<uint4*>(dq + b * sb + t * st + h * sh + c * 8) = o;
+}
+
+// LSE merge.  16 threads per (b, t, h) row, each 8 elements (16 bytes) of both inputs.
+template <bool kBf16>
+__global__ void merge_kernel(const rswa_merge_params_t p, long long n_vec) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const unsigned live = __activemask();
+  const int c = i & 15;
+  const long long row = i >> 4;
+  const int h = row % p.n_heads;
+  const long long bt = row / p.n_heads;
+  const int t = bt % p.q_len;
+  const long long b = bt / p.q_len;
+  const long long li = b * p.lse_stride_b + h * p.lse_stride_h + t;
+  const float la = p.lse_a[li], lb = p.lse_b[li];
+  const float mx = fmaxf(la, lb);
+  float wa, wb, l;
+  if (mx == -INFINITY) {
+    wa = wb = 0.f;
+    l = -INFINITY;
+  } else {
+    const float ea = __expf(la - mx), eb = __expf(lb - mx);
+    const float inv = 1.f / (ea + eb);
+    wa = ea * inv;
+    wb = eb * inv;
+    l = mx + __logf(ea + eb);
+  }
+  const uint4 a = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.o_a) + b * p.oa_stride_b +
+                                                  t * p.oa_stride_t + h * p.oa_stride_h + c * 8);
+  const uint4 bb = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.o_b) + b * p.ob_stride_b +
+                                                   t * p.ob_stride_t + h * p.ob_stride_h + c * 8);
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {bb.x, bb.y, bb.z, bb.w};
+  uint32_t ow[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 fa = unpack2<kBf16>(aw[k]), fb = unpack2<kBf16>(bw[k]);
+    ow[k] = pack2f<kBf16>(fa.x * wa + fb.x * wb, fa.y * wa + fb.y * wb);
+  }
+  *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + b * p.o_stride_b + t * p.o_stride_t +
+                            h * p.o_stride_h + c * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  // all 16 threads of the row have read la/lb (in place is allowed); one writes
+  __syncwarp(live);
+  if (c == 0) p.lse[li] = l;
+}
+
+// acc += recv; 4 elements per thread.  kind: 0 bf16, 1 fp16, 2 float
+template <int kKind>
+__global__ void halo_acc_kernel(float* __restrict__ acc, long long acc_sb, const void* __restrict__ recv,
+                                long long recv_sb, long long vec_per_batch, long long n_vec) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const long long b = i / vec_per_batch, v = i % vec_per_batch;
+  float4* a = reinterpret_cast<float4*>(acc + b * acc_sb) + v;
+  float4 x = *a;
+  if constexpr (kKind == 2) {
+    const float4 r = *(reinterpret_cast<const float4*>(static_cast<const float*>(recv) + b * recv_sb) + v);
+    x.x += r.x; x.y += r.y; x.z += r.z; x.w += r.w;
+  } else {
+    const uint2 r = *(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(recv) + b * recv_sb) + v);
+    const float2 r0 = unpack2<kKind == 0>(r.x), r1 = unpack2<kKind == 0>(r.y);
+    x.x += r0.x; x.y += r0.y; x.z += r1.x; x.w += r1.y;
+  }
+  *a = x;
+}
+
+template <bool kBf16>
+__global__ void cast_kernel(uint16_t* __restrict__ dst, long long dst_sb, const float* __restrict__ src,
+                            long long src_sb, long long vec_per_batch, long long n_vec) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const long long b = i / vec_per_batch, v = i % vec_per_batch;
+  const float4 x = *(reinterpret_cast<const float4*>(src + b * src_sb) + v);
+  uint2 o;
+  o.x = pack2f<kBf16>(x.x, x.y);
+  o.y = pack2f<kBf16>(x.z, x.w);
+  *(reinterpret_cast<uint2*>(dst + b * dst_sb) + v) = o;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: launch: %s", what, cudaGetErrorString(e));
+    return RSWA_E_CUDA;
+  }
+  return RSWA_OK;
+}
+
+}  // namespace
+
+int launch_delta(const rswa_bwd_params_t& p, float* delta, int q_len_pad, cudaStream_t stream) {
+  const rswa_geom_t& g = p.g;
+  const long long rows = static_cast<long long>(g.batch) * g.q_len * g.n_q_heads;
+  const int threads = 256;
+  const long long blocks = (rows * 32 + threads - 1) / threads;
+  auto kern = g.dtype == RSWA_DTYPE_BF16 ? delta_kernel<true> : delta_kernel<false>;
+  kern<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+      static_cast<const uint16_t*>(p.out), p.o_stride_b, p.o_stride_t, p.o_stride_h,
+      static_cast<const uint16_t*>(p.dout), p.do_stride_b, p.do_stride_t, p.do_stride_h, delta, g.batch, g.q_len,
+      g.n_q_heads, q_len_pad);
+  return check_launch("rswa_bwd(delta)");
+}
+
+int launch_dq_convert(const rswa_bwd_params_t& p, const float* dq_acc, cudaStream_t stream) {
+  const rswa_geom_t& g = p.g;
+  const long long n_vec = static_cast<long long>(g.batch) * g.q_len * g.n_q_heads * 16;
+  const int threads = 256;
+  auto kern = g.dtype == RSWA_DTYPE_BF16 ? dq_convert_kernel<true> : dq_convert_kernel<false>;
+  kern<<<static_cast<unsigned>((n_vec + threads - 1) / threads), threads, 0, stream>>>(
+      dq_acc, static_cast<uint16_t*>(p.dq), p.dq_stride_b, p.dq_stride_t, p.dq_stride_h, g.q_len, g.n_q_heads,
+      n_vec, g.softmax_scale);
+  return check_launch("rswa_bwd(dq convert)");
+}
+
+}  // namespace rswa
+
+using namespace rswa;
+
+extern "C" int rswa_merge(const rswa_merge_params_t* p, void* stream) {
+  if (!p || !p->o_a || !p->o_b || !p->o || !p->lse_a || !p->lse_b || !p->lse) {
+    set_error("rswa_merge: null argument");
+    return RSWA_E_ARG;
+  }
+  if (p->head_dim != kHeadDim || (p->dtype != RSWA_DTYPE_BF16 && p->dtype != RSWA_DTYPE_FP16)) {
+    set_error("rswa_merge: head_dim must be 128 and dtype bf16/fp16");
+    return RSWA_E_UNSUPPORTED;
+  }
+  if (p->batch <= 0 || p->q_len <= 0 || p->n_heads <= 0) {
+    set_error("rswa_merge: extents must be positive");
+    return RSWA_E_ARG;
+  }
+  const long long strides[9] = {p->oa_stride_b, p->oa_stride_t, p->oa_stride_h, p->ob_stride_b, p->ob_stride_t,
+                                p->ob_stride_h, p->o_stride_b,  p->o_stride_t,  p->o_stride_h};
+  for (long long s : strides) {
+    if (s % 8) {
+      set_error("rswa_merge: strides must be multiples of 8 elements");
+      return RSWA_E_ARG;
+    }
+  }
+  if ((reinterpret_cast<uintptr_t>(p->o_a) | reinterpret_cast<uintptr_t>(p->o_b) |
+       reinterpret_cast<uintptr_t>(p->o)) & 15) {
+    set_error("rswa_merge: pointers must be 16-byte aligned");
+    return RSWA_E_ARG;
+  }
+  const long long n_vec = static_cast<long long>(p->batch) * p->q_len * p->n_heads * 16;
+  const int threads = 256;
+  auto kern = p->dtype == RSWA_DTYPE_BF16 ? merge_kernel<true> : merge_kernel<false>;
+  kern<<<static_cast<unsigned>((n_vec + threads - 1) / threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      *p, n_vec);
+  return check_launch("rswa_merge");
+}
+
+extern "C" int rswa_halo_accumulate(float* acc, int64_t acc_stride_b, const void* recv, int64_t recv_stride_b,
+                                    int32_t recv_dtype, int32_t batch, int64_t elems_per_batch, void* stream) {
+  if (!acc || !recv || batch <= 0 || elems_per_batch <= 0 || (elems_per_batch % 4) || (acc_stride_b % 4) ||
+      (recv_stride_b % 4) || recv_dtype < 0 || recv_dtype > 2 || (reinterpret_cast<uintptr_t>(acc) & 15) ||
+      (reinterpret_cast<uintptr_t>(recv) & 15)) {
+    set_error("rswa_halo_accumulate: bad argument (need 16-byte alignment and multiples of 4 elements)");
+    return RSWA_E_ARG;
+  }
+  const long long vpb = elems_per_batch / 4, n_vec = vpb * batch;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((n_vec + threads - 1) / threads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (recv_dtype == 0) halo_acc_kernel<0><<<blocks, threads, 0, s>>>(acc, acc_stride_b, recv, recv_stride_b, vpb, n_vec);
+  else if (recv_dtype == 1) halo_acc_kernel<1><<<blocks, threads, 0, s>>>(acc, acc_stride_b, recv, recv_stride_b, vpb, n_vec);
+  else halo_acc_kernel<2><<<blocks, threads, 0, s>>>(acc, acc_stride_b, recv, recv_stride_b, vpb, n_vec);
+  return check_launch("rswa_halo_accumulate");
+}
+
+extern "C" int rswa_cast_from_f32(void* dst, int64_t dst_stride_b, const float* src, int64_t src_stride_b,
+                                  int32_t dtype, int32_t batch, int64_t elems_per_batch, void* stream) {
+  if (!dst || !src || batch <= 0 || elems_per_batch <= 0 || (elems_per_batch % 4) || (dst_stride_b % 4) ||
+      (src_stride_b % 4) || (dtype != 0 && dtype != 1) || (reinterpret_cast<uintptr_t>(dst) & 7) ||
+      (reinterpret_cast<uintptr_t>(src) & 15)) {
+    set_error("rswa_cast_from_f32: bad argument");
+    return RSWA_E_ARG;
+  }
+  const long long vpb = elems_per_batch / 4, n_vec = vpb * batch;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((n_vec + threads - 1) / threads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0) cast_kernel<true><<<blocks, threads, 0, s>>>(static_cast<uint16_t*>(dst), dst_stride_b, src, src_stride_b, vpb, n_vec);
+  else cast_kernel<false><<<blocks, threads, 0, s>>>(static_cast<uint16_t*>(dst), dst_stride_b, src, src_stride_b, vpb, n_vec);
+  return check_launch("rswa_cast_from_f32");
+}

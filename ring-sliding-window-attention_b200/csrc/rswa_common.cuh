@@ -1,0 +1,97 @@
+// Internal declarations shared by the kernels and the C-ABI layer.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/rswa.h"
+
+namespace rswa {
+
+constexpr int kTile = RSWA_TILE;       // rows of a query tile and of a key tile
+constexpr int kHeadDim = 128;
+constexpr int kBoxBytes = 16384;       // one TMA box: 128 rows x 64 x 16-bit, 128-byte swizzle
+constexpr int kTileBytes = 2 * kBoxBytes;
+constexpr int kMaxEntries = 2 * RSWA_MAX_SPANS;
+
+// device-side error codes written to the status word
+enum : int {
+  kErrWaitProducer = 101,
+  kErrWaitMma = 102,
+  kErrWaitSoftmax = 103,
+  kErrWaitEpilogue = 104,
+};
+
+struct FwdKernelParams {
+  CUtensorMap q_map;
+  CUtensorMap k_map[RSWA_MAX_SPANS];
+  CUtensorMap v_map[RSWA_MAX_SPANS];
+  int span_pos[RSWA_MAX_SPANS];
+  int span_len[RSWA_MAX_SPANS];
+  int n_spans;
+  int batch, q_len, hq, hkv;
+  int q_pos_start, window, n_sink;
+  float scale_log2;  // softmax_scale * log2(e)
+  const int* cu;
+  int n_seqs;
+  void* out;
+  long long o_sb, o_st, o_sh;
+  float* lse;
+  long long l_sb, l_sh;
+  int q_tile_begin, n_q_tiles;
+  int* status;
+};
+
+struct BwdKernelParams {
+  CUtensorMap q_map;
+  CUtensorMap do_map;
+  CUtensorMap k_map[RSWA_MAX_SPANS];
+  CUtensorMap v_map[RSWA_MAX_SPANS];
+  int span_pos[RSWA_MAX_SPANS];
+  int span_len[RSWA_MAX_SPANS];
+  int span_tile0[RSWA_MAX_SPANS + 1];  // prefix sum of key tiles per span
+  void* dk[RSWA_MAX_SPANS];
+  void* dv[RSWA_MAX_SPANS];
+  long long dkv_sb[RSWA_MAX_SPANS], dkv_st[RSWA_MAX_SPANS], dkv_sh[RSWA_MAX_SPANS];
+  int grad_fp32[RSWA_MAX_SPANS];
+  int n_spans;
+  int batch, q_len, hq, hkv;
+  int q_pos_start, window, n_sink;
+  float scale_log2;
+  float scale;
+  const int* cu;
+  int n_seqs;
+  const float* lse;
+  long long l_sb, l_sh;
+  const float* delta;  // [batch, hq, q_len_pad]
+  long long d_sb, d_sh;
+  float* dq_acc;  // [batch, q_len, hq, 128] contiguous fp32
+  int* status;
+};
+
+// Sequence [start, end) containing global position p.  cu has n_seqs + 1 entries.
+__device__ __forceinline__ void seq_of(const int* __restrict__ cu, int n_seqs, int p, int& start,
+                                       int& end) {
+  if (cu == nullptr) {
+    start = 0;
+    end = 0x7fffffff;
+    return;
+  }
+  int lo = 0, hi = n_seqs;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (__ldg(cu + mid) <= p) lo = mid; else hi = mid - 1;
+  }
+  start = __ldg(cu + lo);
+  end = (lo < n_seqs) ? __ldg(cu + lo + 1) : 0x7fffffff;
+}
+
+// host side -------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+// 4-D map over a [batch, tokens, heads, 128] 16-bit tensor (strides in elements), box = 64
+// elements x 1 head x 128 tokens x 1 batch, 128-byte swizzle, zero fill out of bounds.
+int make_tile_map(CUtensorMap* map, const void* base, int dtype, int batch, int tokens, int heads,
+                  long long sb, long long st, long long sh);
+int check_geom(const rswa_geom_t& g, bool need_grads);
+
+}  // namespace rswa

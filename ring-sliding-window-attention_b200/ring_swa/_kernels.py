@@ -1,0 +1,248 @@
+"""Torch-tensor front end of the C ABI: builds the parameter structs and launches on the current stream.
+
+All tensors are 4-D here, [batch, tokens, heads, 128]; packed (varlen) callers add a leading batch of 1.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _C
+
+HEAD_DIM = 128
+TILE = _C.TILE
+
+
+@dataclass
+class KVSpan:
+    """A run of consecutive tokens' K/V held in one buffer (own tokens, a received halo, the sink)."""
+    k: torch.Tensor                     # [B, L, Hkv, D]
+    v: torch.Tensor
+    pos_start: int                      # global position of token 0
+    dk: Optional[torch.Tensor] = None   # backward outputs, same shape; fp32 or the input dtype
+    dv: Optional[torch.Tensor] = None
+
+    @property
+    def length(self) -> int:
+        return self.k.shape[1]
+
+
+_status = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Device word the kernels raise when a bounded device-side wait runs out."""
+    key = (device.type, device.index)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_device_status(device: Optional[torch.device] = None) -> None:
+    """Synchronises and raises if any kernel reported a device-side time-out since the last check."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise RuntimeError(f"ring_swa kernel reported device-side error code {code} (a bounded wait ran out)")
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return _C.DTYPE_BF16
+    if t.dtype == torch.float16:
+        return _C.DTYPE_FP16
+    raise ValueError(f"ring_swa kernels take bfloat16 or float16 tensors, got {t.dtype}")
+
+
+def _check4(name: str, t: torch.Tensor) -> None:
+    if t.dim() != 4 or t.shape[-1] != HEAD_DIM:
+        raise ValueError(f"{name} must be [batch, tokens, heads, {HEAD_DIM}], got {tuple(t.shape)}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: ring_swa has no CPU path")
+    if t.stride(-1) != 1:
+        raise ValueError(f"{name} must be contiguous in the head dimension")
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _fill_geom(g: _C.Geom, q: torch.Tensor, spans: Sequence[KVSpan], window: int, n_sink: int, scale: float,
+               q_pos_start: int, cu_seqlens: Optional[torch.Tensor], grads: bool) -> None:
+    if len(spans) > _C.RSWA_MAX_SPANS:
+        raise ValueError(f"at most {_C.RSWA_MAX_SPANS} KV spans per call")
+    B, S, Hq, D = q.shape
+    g.dtype = _dtype_code(q)
+    g.batch, g.q_len, g.n_q_heads, g.head_dim = B, S, Hq, D
+    g.n_kv_heads = spans[0].k.shape[2] if spans else Hq
+    g.q_pos_start = int(q_pos_start)
+    g.window = int(window)
+    g.n_sink = int(n_sink)
+    g.softmax_scale = float(scale)
+    if cu_seqlens is not None:
+        if cu_seqlens.dtype != torch.int32 or not cu_seqlens.is_cuda or not cu_seqlens.is_contiguous():
+            raise ValueError("cu_seqlens must be a contiguous int32 CUDA tensor")
+        g.cu_seqlens = cu_seqlens.data_ptr()
+        g.n_seqs = cu_seqlens.numel() - 1
+    else:
+        g.cu_seqlens = None
+        g.n_seqs = 0
+    g.n_spans = len(spans)
+    for i, s in enumerate(spans):
+        _check4("k", s.k)
+        _check4("v", s.v)
+        if s.k.dtype != q.dtype or s.v.dtype != q.dtype:
+            raise ValueError("q, k and v must have the same dtype")
+        if s.k.shape != s.v.shape or s.k.stride() != s.v.stride():
+            raise ValueError("k and v of a span must have the same shape and strides")
+        if s.k.shape[0] != B or s.k.shape[2] != g.n_kv_heads:
+            raise ValueError("span batch / head count mismatch")
+        c = g.spans[i]
+        c.k, c.v = s.k.data_ptr(), s.v.data_ptr()
+        c.kv_stride_b, c.kv_stride_t, c.kv_stride_h = s.k.stride(0), s.k.stride(1), s.k.stride(2)
+        c.pos_start, c.len = int(s.pos_start), s.k.shape[1]
+        if grads:
+            if s.dk is None or s.dv is None:
+                raise ValueError("backward needs dk and dv for every span")
+            if s.dk.shape != s.k.shape or s.dv.shape != s.k.shape or s.dk.stride() != s.dv.stride():
+                raise ValueError("dk/dv must match k in shape and each other in strides")
+            if s.dk.dtype != s.dv.dtype or s.dk.dtype not in (torch.float32, q.dtype):
+                raise ValueError("dk/dv must be float32 or the input dtype")
+            c.dk, c.dv = s.dk.data_ptr(), s.dv.data_ptr()
+            c.dkv_stride_b, c.dkv_stride_t, c.dkv_stride_h = s.dk.stride(0), s.dk.stride(1), s.dk.stride(2)
+            c.grad_fp32 = 1 if s.dk.dtype == torch.float32 else 0
+
+
+def fwd(q: torch.Tensor, spans: Sequence[KVSpan], window: int, n_sink: int, scale: float, q_pos_start: int = 0,
+        cu_seqlens: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+        lse: Optional[torch.Tensor] = None, q_tiles: Optional[Tuple[int, int]] = None
+        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """out [B,S,Hq,D] (input dtype) and lse [B,Hq,S] (fp32) over the given spans."""
+    _check4("q", q)
+    B, S, Hq, D = q.shape
+    if out is None:
+        out = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
+    if lse is None:
+        lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    p = _C.FwdParams()
+    _fill_geom(p.g, q, spans, window, n_sink, scale, q_pos_start, cu_seqlens, grads=False)
+    p.q = q.data_ptr()
+    p.q_stride_b, p.q_stride_t, p.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
+    p.out = out.data_ptr()
+    p.o_stride_b, p.o_stride_t, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    if lse.dtype != torch.float32 or lse.stride(2) != 1:
+        raise ValueError("lse must be float32 [B, Hq, S] with contiguous tokens")
+    p.lse = lse.data_ptr()
+    p.lse_stride_b, p.lse_stride_h = lse.stride(0), lse.stride(1)
+    p.q_tile_begin, p.q_tile_end = (0, 0) if q_tiles is None else (int(q_tiles[0]), int(q_tiles[1]))
+    if q_tiles is not None and q_tiles[1] <= q_tiles[0]:
+        return out, lse
+    p.status = status_word(q.device).data_ptr()
+    _C.check(_C.lib().rswa_fwd(C.byref(p), _stream()), "rswa_fwd")
+    return out, lse
+
+
+def bwd_workspace(q: torch.Tensor) -> torch.Tensor:
+    B, S, Hq, D = q.shape
+    n = _C.lib().rswa_bwd_workspace_bytes(B, S, Hq, D)
+    if n < 0:
+        raise ValueError("rswa_bwd_workspace_bytes: unsupported shape")
+    return torch.empty(n, dtype=torch.uint8, device=q.device)
+
+
+def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor,
+        dq: torch.Tensor, window: int, n_sink: int, scale: float, q_pos_start: int = 0,
+        cu_seqlens: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+        flags: int = _C.BWD_INIT | _C.BWD_FINISH) -> torch.Tensor:
+    """dq and every span's dk/dv.  Returns the workspace so that a later call can continue it."""
+    for name, t in (("q", q), ("out", out), ("dout", dout), ("dq", dq)):
+        _check4(name, t)
+        if t.dtype != q.dtype or t.shape != q.shape:
+            raise ValueError(f"{name} must match q in dtype and shape")
+    if workspace is None:
+        workspace = bwd_workspace(q)
+    p = _C.BwdParams()
+    _fill_geom(p.g, q, spans, window, n_sink, scale, q_pos_start, cu_seqlens, grads=True)
+    p.q = q.data_ptr()
+    p.q_stride_b, p.q_stride_t, p.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
+    p.out = out.data_ptr()
+    p.o_stride_b, p.o_stride_t, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    p.dout = dout.data_ptr()
+    p.do_stride_b, p.do_stride_t, p.do_stride_h = dout.stride(0), dout.stride(1), dout.stride(2)
+    if lse.dtype != torch.float32 or lse.stride(2) != 1:
+        raise ValueError("lse must be float32 [B, Hq, S] with contiguous tokens")
+    p.lse = lse.data_ptr()
+    p.lse_stride_b, p.lse_stride_h = lse.stride(0), lse.stride(1)
+    p.dq = dq.data_ptr()
+    p.dq_stride_b, p.dq_stride_t, p.dq_stride_h = dq.stride(0), dq.stride(1), dq.stride(2)
+    p.workspace = workspace.data_ptr()
+    p.workspace_bytes = workspace.numel()
+    p.flags = int(flags)
+    p.status = status_word(q.device).data_ptr()
+    _C.check(_C.lib().rswa_bwd(C.byref(p), _stream()), "rswa_bwd")
+    return workspace
+
+
+def merge(o_a: torch.Tensor, lse_a: torch.Tensor, o_b: torch.Tensor, lse_b: torch.Tensor,
+          out: Optional[torch.Tensor] = None, lse_out: Optional[torch.Tensor] = None
+          ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Log-sum-exp merge of two partial results; in place on (o_a, lse_a) unless outputs are given."""
+    _check4("o_a", o_a)
+    _check4("o_b", o_b)
+    out = o_a if out is None else out
+    lse_out = lse_a if lse_out is None else lse_out
+    B, S, H, D = o_a.shape
+    for l in (lse_a, lse_b, lse_out):
+        if l.dtype != torch.float32 or l.shape != (B, H, S) or l.stride() != lse_a.stride() or l.stride(2) != 1:
+            raise ValueError("lse tensors must be float32 [B, H, S] with identical strides")
+    p = _C.MergeParams()
+    p.dtype = _dtype_code(o_a)
+    p.batch, p.q_len, p.n_heads, p.head_dim = B, S, H, D
+    p.o_a, p.o_b, p.o = o_a.data_ptr(), o_b.data_ptr(), out.data_ptr()
+    p.oa_stride_b, p.oa_stride_t, p.oa_stride_h = o_a.stride(0), o_a.stride(1), o_a.stride(2)
+    p.ob_stride_b, p.ob_stride_t, p.ob_stride_h = o_b.stride(0), o_b.stride(1), o_b.stride(2)
+    p.o_stride_b, p.o_stride_t, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    p.lse_a, p.lse_b, p.lse = lse_a.data_ptr(), lse_b.data_ptr(), lse_out.data_ptr()
+    p.lse_stride_b, p.lse_stride_h = lse_a.stride(0), lse_a.stride(1)
+    _C.check(_C.lib().rswa_merge(C.byref(p), _stream()), "rswa_merge")
+    return out, lse_out
+
+
+def _rows(t: torch.Tensor) -> Tuple[int, int, int]:
+    """(batch, batch stride, contiguous elements per batch row) of a [B, ...] tensor."""
+    if t.dim() < 2 or not t[0].is_contiguous():
+        raise ValueError("expected a tensor whose batch rows are contiguous")
+    return t.shape[0], t.stride(0), t[0].numel()
+
+
+def halo_accumulate(acc: torch.Tensor, recv: torch.Tensor) -> None:
+    """acc (fp32) += recv, both [B, L, H, D] with contiguous batch rows."""
+    if acc.dtype != torch.float32 or acc.shape != recv.shape:
+        raise ValueError("halo_accumulate: acc must be float32 and match recv in shape")
+    B, asb, n = _rows(acc)
+    _, rsb, _ = _rows(recv)
+    code = _C.DTYPE_F32 if recv.dtype == torch.float32 else _dtype_code(recv)
+    _C.check(_C.lib().rswa_halo_accumulate(acc.data_ptr(), asb, recv.data_ptr(), rsb, code, B, n, _stream()),
+             "rswa_halo_accumulate")
+
+
+def cast_from_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
+    if src.dtype != torch.float32 or dst.shape != src.shape:
+        raise ValueError("cast_from_f32: src must be float32 and match dst in shape")
+    B, dsb, n = _rows(dst)
+    _, ssb, _ = _rows(src)
+    _C.check(_C.lib().rswa_cast_from_f32(dst.data_ptr(), dsb, src.data_ptr(), ssb, _dtype_code(dst), B, n,
+                                         _stream()), "rswa_cast_from_f32")
+
+
+def selftest_mma(mode: int, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    d = torch.zeros(128, 128, dtype=torch.float32, device=a.device)
+    _C.check(_C.lib().rswa_selftest_mma(mode, a.data_ptr(), b.data_ptr(), d.data_ptr(),
+                                        status_word(a.device).data_ptr(), _stream()), "rswa_selftest_mma")
+    return d

@@ -1,0 +1,123 @@
+"""Host-side plan of one rank's halo and sink exchange.  Pure integer logic, no tensors.
+
+The reference forwards WHOLE K/V blocks hop by hop round the ring for
+C = min(ceil(W / S), cp - 1) rounds (ring_swa/sliding_window/nonvarlen.py:46-49, 70-92) and lets
+each hop's mask case discard what is not visible.  Here every rank works out, from the same
+inputs, exactly which trailing tokens of which earlier rank it can see, and only those travel:
+rank r needs the keys at global positions [max(seq_start, r*S - W), r*S), i.e. the trailing
+min(S, ...) tokens of ranks r-1, r-2, ..., plus (StreamingLLM) the first n_sink tokens of the
+sequence that crosses its left edge when those lie further back
+(ring_swa/streaming_llm/nonvarlen.py:48-55 broadcasts them from group rank 0).
+"""
+from __future__ import annotations
+
+import bisect
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+TILE = 128
+
+
+@dataclass
+class HaloRecv:
+    hop: int          # source is group rank `rank - hop`
+    src: int
+    length: int       # trailing tokens of the source's chunk
+    pos_start: int    # global position of the first of them
+
+
+@dataclass
+class HaloSend:
+    hop: int
+    dst: int
+    length: int       # my trailing tokens
+
+
+@dataclass
+class SinkRecv:
+    owner: int        # group rank that holds the sink tokens
+    pos_start: int    # their global position
+    n: int
+
+
+@dataclass
+class SinkSend:
+    dst: int
+    offset: int       # local token offset of the sink tokens in my chunk
+    n: int
+
+
+@dataclass
+class RingPlan:
+    cp: int
+    rank: int
+    seq_per_rank: int
+    window: int
+    n_sink: int
+    halo_recv: List[HaloRecv] = field(default_factory=list)
+    halo_send: List[HaloSend] = field(default_factory=list)
+    sink_recv: Optional[SinkRecv] = None
+    sink_send: List[SinkSend] = field(default_factory=list)
+    # query tiles [halo_tile_end, n_tiles) see local keys only (and the sink)
+    halo_tile_end: int = 0
+
+    @property
+    def q_pos_start(self) -> int:
+        return self.rank * self.seq_per_rank
+
+    @property
+    def n_tiles(self) -> int:
+        return (self.seq_per_rank + TILE - 1) // TILE
+
+
+def seq_start_of(pos: int, cu: Optional[Sequence[int]]) -> int:
+    """Start of the sequence that contains global position `pos` (0 when batch rows are the sequences)."""
+    if cu is None:
+        return 0
+    i = bisect.bisect_right(cu, pos) - 1
+    i = max(0, min(i, len(cu) - 2))
+    return int(cu[i])
+
+
+def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv], Optional[SinkRecv]]:
+    """What rank r must receive: (lowest needed window position, halos, sink)."""
+    left = r * S
+    s_cross = seq_start_of(left, cu)
+    lo = max(s_cross, left - W, 0)
+    halos: List[HaloRecv] = []
+    h = 1
+    while r - h >= 0:
+        a, b = (r - h) * S, (r - h + 1) * S
+        if b <= lo:
+            break
+        start = max(lo, a)
+        halos.append(HaloRecv(hop=h, src=r - h, length=b - start, pos_start=start))
+        h += 1
+    sink = None
+    if n_sink > 0 and s_cross < lo:
+        owner = s_cross // S
+        end = min(s_cross + n_sink, lo, (owner + 1) * S)
+        if end > s_cross:
+            sink = SinkRecv(owner=owner, pos_start=s_cross, n=end - s_cross)
+    return lo, halos, sink
+
+
+def make_plan(cp: int, rank: int, S: int, W: int, n_sink: int, cu: Optional[Sequence[int]]) -> RingPlan:
+    """Plan for `rank`; every rank derives the matching sends from the other ranks' needs."""
+    if cp < 1 or not (0 <= rank < cp):
+        raise ValueError(f"invalid context-parallel geometry: cp_size={cp}, cp_local_rank={rank}")
+    if S <= 0 or W < 0 or n_sink < 0:
+        raise ValueError("sequence length per rank must be positive, window and n_sink non-negative")
+    plan = RingPlan(cp=cp, rank=rank, seq_per_rank=S, window=W, n_sink=n_sink)
+    lo, plan.halo_recv, plan.sink_recv = _needs(rank, S, W, n_sink, cu)
+    for r in range(rank + 1, cp):
+        _, halos, sink = _needs(r, S, W, n_sink, cu)
+        for hr in halos:
+            if hr.src == rank:
+                plan.halo_send.append(HaloSend(hop=hr.hop, dst=r, length=hr.length))
+        if sink is not None and sink.owner == rank:
+            plan.sink_send.append(SinkSend(dst=r, offset=sink.pos_start - rank * S, n=sink.n))
+    if plan.halo_recv:
+        # local query a (position rank*S + a) reaches below the chunk iff a < W
+        plan.halo_tile_end = min(plan.n_tiles, (min(W, S) + TILE - 1) // TILE)
+    return plan

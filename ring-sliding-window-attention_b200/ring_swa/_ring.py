@@ -1,0 +1,232 @@
+"""The one autograd function behind the four public entry points.
+
+Forward, on rank r of cp (sequence split contiguously, chunk i on group rank i):
+  1. post the sink exchange and the halo exchange (torch.distributed P2P, NCCL over NVLink);
+  2. while they fly, run the query tiles that only see local keys;
+  3. when the halo has landed, run the remaining tiles over sink | halo | local in ONE pass
+     (no per-hop partial results), or, when the window spans the whole chunk (W >= S), run the
+     halo as a second partial and fold it in with the log-sum-exp merge kernel.
+Backward mirrors it: K/V gradients of halo (and remote sink) tokens are computed first and sent
+back to their owners while the local part runs; the owner adds them in fp32 and rounds once.
+
+This replaces RingSlidingWindowAttn / RingSlidingWindowAttnVarlen / RingStreamingLLMAttn /
+RingStreamingLLMVarlen of the reference (ring_swa/sliding_window/nonvarlen.py:17-338,
+varlen.py:19-359, ring_swa/streaming_llm/nonvarlen.py:20-397, varlen.py:20-473) and the naive
+single-GPU StreamingLLM functions (ring_swa/streaming_llm/naive.py:11-210).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from . import _C
+from . import _kernels as K
+from ._plan import RingPlan, make_plan
+
+# dtype the halo / sink gradients travel in (None: the input dtype, like the per-hop partials of
+# ring_swa/sliding_window/nonvarlen.py:194-195; torch.float32 to send them unrounded)
+HALO_GRAD_WIRE_DTYPE = None
+
+
+@dataclass
+class RingCtx:
+    """Who is where.  `group` is None on a single GPU."""
+    group: Optional[dist.ProcessGroup]
+    cp: int
+    rank: int
+    prev_global: Optional[int]
+    next_global: Optional[int]
+
+    def global_rank(self, group_rank: int) -> int:
+        if group_rank == self.rank + 1 and self.next_global is not None:
+            return self.next_global
+        if group_rank == self.rank - 1 and self.prev_global is not None:
+            return self.prev_global
+        return dist.get_global_rank(self.group, group_rank)
+
+
+def _exchange(ops: List[dist.P2POp]):
+    return dist.batch_isend_irecv(ops) if ops else []
+
+
+def _wait(works) -> None:
+    for w in works:
+        w.wait()
+
+
+def _dense(t: torch.Tensor) -> torch.Tensor:
+    """The kernels address tensors through TMA descriptors: strides must be positive multiples of
+    16 bytes with the head dimension contiguous.  Anything else (expanded grads, odd slices) is copied."""
+    ok = t.stride(-1) == 1 and all(st > 0 and st % 8 == 0 for st in t.stride()[:-1]) and t.data_ptr() % 16 == 0
+    return t if ok else t.contiguous()
+
+
+def _pack_tail(k4: torch.Tensor, v4: torch.Tensor, length: int) -> torch.Tensor:
+    """[2, B, L, Hkv, D] copy of the trailing `length` tokens of K and V (one message)."""
+    S = k4.shape[1]
+    buf = torch.empty((2, k4.shape[0], length) + tuple(k4.shape[2:]), dtype=k4.dtype, device=k4.device)
+    buf[0].copy_(k4[:, S - length:])
+    buf[1].copy_(v4[:, S - length:])
+    return buf
+
+
+class RingAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, window: int, n_sink: int, softmax_scale: float,
+                cu_seqlens: Optional[torch.Tensor], cu_host: Optional[Sequence[int]], ring: RingCtx):
+        varlen = cu_seqlens is not None
+        q4, k4, v4 = (_dense(x).unsqueeze(0) if varlen else _dense(x) for x in (q, k, v))
+        if v4.stride() != k4.stride():
+            v4 = v4.contiguous()
+            k4 = k4.contiguous()
+        B, S, Hq, D = q4.shape
+        plan = make_plan(ring.cp, ring.rank, S, window, n_sink, cu_host)
+        if 1 + len(plan.halo_recv) + (plan.sink_recv is not None) > _C.RSWA_MAX_SPANS:
+            raise ValueError("window reaches over more ranks than one call supports "
+                             f"({len(plan.halo_recv)} hops)")
+        pos0 = plan.q_pos_start
+        local = K.KVSpan(k4, v4, pos0)
+
+        # -- post the exchanges
+        sink_ops, halo_ops, keep = [], [], []
+        sink_span = None
+        for s in plan.sink_send:
+            buf = torch.stack([k4[:, s.offset:s.offset + s.n], v4[:, s.offset:s.offset + s.n]])
+            keep.append(buf)
+            sink_ops.append(dist.P2POp(dist.isend, buf, ring.global_rank(s.dst), ring.group))
+        if plan.sink_recv is not None:
+            sr = plan.sink_recv
+            sbuf = torch.empty((2, B, sr.n) + tuple(k4.shape[2:]), dtype=k4.dtype, device=k4.device)
+            sink_ops.append(dist.P2POp(dist.irecv, sbuf, ring.global_rank(sr.owner), ring.group))
+            sink_span = K.KVSpan(sbuf[0], sbuf[1], sr.pos_start)
+        packed = {}
+        for s in plan.halo_send:
+            if s.length not in packed:
+                packed[s.length] = _pack_tail(k4, v4, s.length)
+            halo_ops.append(dist.P2POp(dist.isend, packed[s.length], ring.global_rank(s.dst), ring.group))
+        halo_spans = []
+        for r in plan.halo_recv:
+            hbuf = torch.empty((2, B, r.length) + tuple(k4.shape[2:]), dtype=k4.dtype, device=k4.device)
+            halo_ops.append(dist.P2POp(dist.irecv, hbuf, ring.global_rank(r.src), ring.group))
+            halo_spans.append(K.KVSpan(hbuf[0], hbuf[1], r.pos_start))
+        sink_works = _exchange(sink_ops)
+        halo_works = _exchange(halo_ops)
+
+        # -- compute
+        out = torch.empty_like(q4)
+        lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q4.device)
+        args = dict(window=window, n_sink=n_sink, scale=softmax_scale, q_pos_start=pos0, cu_seqlens=cu_seqlens)
+        _wait(sink_works)
+        near = ([sink_span] if sink_span is not None else []) + [local]
+        if not halo_spans:
+            K.fwd(q4, near, out=out, lse=lse, **args)
+        elif window < S:
+            nb = plan.halo_tile_end
+            K.fwd(q4, near, out=out, lse=lse, q_tiles=(nb, plan.n_tiles), **args)
+            _wait(halo_works)
+            spans = ([sink_span] if sink_span is not None else []) + halo_spans[::-1] + [local]
+            K.fwd(q4, spans, out=out, lse=lse, q_tiles=(0, nb), **args)
+        else:
+            K.fwd(q4, near, out=out, lse=lse, **args)
+            _wait(halo_works)
+            o2, lse2 = K.fwd(q4, halo_spans[::-1], **args)
+            K.merge(out, lse, o2, lse2)
+        _wait(halo_works)
+
+        ctx.save_for_backward(q4, k4, v4, out, lse, cu_seqlens,
+                              *[t for s in halo_spans for t in (s.k, s.v)],
+                              *([sink_span.k, sink_span.v] if sink_span is not None else []))
+        ctx.plan, ctx.ring, ctx.args, ctx.varlen = plan, ring, args, varlen
+        ctx.keep_alive = keep + list(packed.values())
+        return out.squeeze(0) if varlen else out
+
+    @staticmethod
+    def backward(ctx, dout):
+        plan: RingPlan = ctx.plan
+        ring: RingCtx = ctx.ring
+        saved = ctx.saved_tensors
+        q, k, v, out, lse, cu_seqlens = saved[:6]
+        rest = list(saved[6:])
+        varlen = ctx.varlen
+        q4, k4, v4 = q, k, v
+        do4 = _dense(dout).unsqueeze(0) if varlen else _dense(dout)
+        B, S, Hq, D = q4.shape
+        args = dict(ctx.args)
+        args["cu_seqlens"] = cu_seqlens
+        wire = HALO_GRAD_WIRE_DTYPE or q4.dtype
+
+        def grad_pair(shape):
+            g = torch.empty((2,) + tuple(shape), dtype=wire, device=q4.device)
+            return g
+
+        remote, remote_grads = [], []
+        for r in plan.halo_recv:
+            hk, hv = rest.pop(0), rest.pop(0)
+            g = grad_pair(hk.shape)
+            remote.append(K.KVSpan(hk, hv, r.pos_start, dk=g[0], dv=g[1]))
+            remote_grads.append(g)
+        sink_grad = None
+        if plan.sink_recv is not None:
+            sk, sv = rest.pop(0), rest.pop(0)
+            sink_grad = grad_pair(sk.shape)
+            remote.insert(0, K.KVSpan(sk, sv, plan.sink_recv.pos_start, dk=sink_grad[0], dv=sink_grad[1]))
+
+        dq4 = torch.empty_like(q4)
+        ws = K.bwd_workspace(q4)
+        ops, recvs = [], []
+        if remote:
+            K.bwd(q4, remote, out, lse, do4, dq4, workspace=ws, flags=_C.BWD_INIT, **args)
+            for r, g in zip(plan.halo_recv, remote_grads):
+                ops.append(dist.P2POp(dist.isend, g, ring.global_rank(r.src), ring.group))
+            if sink_grad is not None:
+                ops.append(dist.P2POp(dist.isend, sink_grad, ring.global_rank(plan.sink_recv.owner), ring.group))
+        for s in plan.halo_send:
+            g = grad_pair((B, s.length) + tuple(k4.shape[2:]))
+            ops.append(dist.P2POp(dist.irecv, g, ring.global_rank(s.dst), ring.group))
+            recvs.append((S - s.length, s.length, g))
+        for s in plan.sink_send:
+            g = grad_pair((B, s.n) + tuple(k4.shape[2:]))
+            ops.append(dist.P2POp(dist.irecv, g, ring.global_rank(s.dst), ring.group))
+            recvs.append((s.offset, s.n, g))
+        works = _exchange(ops)
+
+        dk4, dv4 = torch.empty_like(k4), torch.empty_like(v4)
+        if recvs:
+            acc = torch.empty((2,) + tuple(k4.shape), dtype=torch.float32, device=k4.device)
+            local = K.KVSpan(k4, v4, plan.q_pos_start, dk=acc[0], dv=acc[1])
+        else:
+            acc = None
+            local = K.KVSpan(k4, v4, plan.q_pos_start, dk=dk4, dv=dv4)
+        flags = _C.BWD_FINISH | (0 if remote else _C.BWD_INIT)
+        K.bwd(q4, [local], out, lse, do4, dq4, workspace=ws, flags=flags, **args)
+        _wait(works)
+        if acc is not None:
+            for off, n, g in recvs:
+                K.halo_accumulate(acc[0][:, off:off + n], g[0])
+                K.halo_accumulate(acc[1][:, off:off + n], g[1])
+            K.cast_from_f32(dk4, acc[0])
+            K.cast_from_f32(dv4, acc[1])
+        if varlen:
+            dq4, dk4, dv4 = dq4.squeeze(0), dk4.squeeze(0), dv4.squeeze(0)
+        return dq4, dk4, dv4, None, None, None, None, None, None
+
+
+def ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank) -> RingCtx:
+    """Argument defaulting of ring_swa/sliding_window/nonvarlen.py:388-395."""
+    if cp_group is None:
+        return RingCtx(None, 1, 0, None, None)
+    if cp_size is None:
+        cp_size = dist.get_world_size(cp_group)
+    if cp_local_rank is None:
+        cp_local_rank = dist.get_rank(group=cp_group)
+    return RingCtx(cp_group, int(cp_size), int(cp_local_rank), cp_prev_global_rank, cp_next_global_rank)
+
+
+def attention(q, k, v, window_size: int, n_sink: int, softmax_scale: Optional[float],
+              cu_seqlens: Optional[torch.Tensor], cu_host: Optional[Sequence[int]], ring: RingCtx):
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    return RingAttn.apply(q, k, v, int(window_size), int(n_sink), float(softmax_scale), cu_seqlens, cu_host, ring)

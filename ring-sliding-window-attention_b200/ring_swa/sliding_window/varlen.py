@@ -1,0 +1,47 @@
+"""ring_sliding_window_attn_varlen: same signature as ring_swa/sliding_window/varlen.py:362-374."""
+from typing import Optional
+
+import torch
+from torch.distributed import ProcessGroup
+
+from .._ring import attention, ring_ctx
+
+
+def _varlen_prologue(q, k, v, cu_seqlens, cp_size):
+    assert q.dim() == 3 and k.dim() == 3 and v.dim() == 3, "q, k, v must be [seq_len, heads, head_dim]"
+    assert q.shape[0] == k.shape[0] == v.shape[0], "Sequence length must be the same"
+    assert q.shape[1] % k.shape[1] == 0, "Number of query heads must be divisible by number of key/value heads"
+    # one device-to-host copy, where the reference has its own (and several more further down):
+    # the global cumulative lengths drive the halo plan on the host
+    cu_host = [int(x) for x in cu_seqlens.tolist()]
+    # ring_swa/sliding_window/varlen.py:401-403; evaluated before cp_group is looked at, so a
+    # missing cp_size raises TypeError there as well
+    assert q.shape[0] == cu_host[-1] // cp_size, "cu_seqlens does not match with sequence length per rank"
+    if cu_seqlens.dtype != torch.int32:
+        cu_seqlens = cu_seqlens.to(torch.int32)
+    return cu_seqlens.contiguous(), cu_host
+
+
+def ring_sliding_window_attn_varlen(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    window_size: int,
+    cu_seqlens: torch.Tensor,
+    cp_group: Optional[ProcessGroup] = None,
+    cp_size: Optional[int] = None,
+    cp_local_rank: Optional[int] = None,
+    cp_prev_global_rank: Optional[int] = None,
+    cp_next_global_rank: Optional[int] = None,
+    softmax_scale: Optional[float] = None,
+) -> torch.Tensor:
+    """Ring sliding window attention over packed variable-length sequences.
+
+    q [seq_len, num_q_heads, head_dim]; k, v [seq_len, num_kv_heads, head_dim]: this rank's equal share of
+    the packed token axis.  cu_seqlens holds the cumulative lengths of ALL sequences across all ranks
+    ([batch_size + 1], int32, on the device).  Other arguments as in ring_sliding_window_attn.
+    Returns [seq_len, num_q_heads, head_dim].
+    """
+    cu_seqlens, cu_host = _varlen_prologue(q, k, v, cu_seqlens, cp_size)
+    ring = ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank)
+    return attention(q, k, v, window_size, 0, softmax_scale, cu_seqlens, cu_host, ring)
