@@ -1,0 +1,371 @@
+"""Benchmark: ring sliding-window attention forward + backward, tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+
+A step is one forward + backward of the public API over one batch of synthetic N(0,1) bf16 inputs.
+The default workload is BASELINE configuration 2 (B=2, S=32768, 32 q heads / 32 kv heads, D=128,
+window 1000).  With --gpus N > 1 (launched under torch.distributed.run, one rank per GPU) the
+sequence is sharded over the ranks: by default each rank keeps the 1-GPU chunk (S_global = 32768*N,
+"scaling": "weak"); `--scaling strong` keeps S_global = 32768 and splits it.
+
+One JSON line is printed by rank 0.  `value` is timed with inputs resident in HBM; `e2e` adds the
+host->device copy of q, k, v, dO from pinned memory and the device->host copy of out, dq, dk, dv every
+step; `roofline` is the backward kernel (the dominant one) timed with CUDA events on its stream;
+`cpu_baseline` is the dense torch CPU restatement of the reference's test oracle on a bounded slice.
+
+`--impl reference` times that CPU restatement alone (the reference's own attention arithmetic lives in
+flash-attn CUDA kernels and has no CPU path; its naive torch oracle is what runs on host cores).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "ring-sliding-window-attention_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+D = 128
+WORKLOADS = {
+    # name: fn, batch, S (1-GPU tokens per batch row), Hq, Hkv, window, n_sink, seed
+    "cfg2": dict(fn="ring_sliding_window_attn", B=2, S=32768, Hq=32, Hkv=32, W=1000, n_sink=0, seed=1),
+    "cfg3": dict(fn="ring_sliding_window_attn_varlen", B=1, S=65536, Hq=32, Hkv=8, W=4096, n_sink=0, seed=2),
+    "cfg4": dict(fn="ring_streaming_llm_attn", B=1, S=131072, Hq=32, Hkv=8, W=8192, n_sink=1, seed=3),
+    "cfg5": dict(fn="ring_sliding_window_attn", B=1, S=262144, Hq=64, Hkv=8, W=65536, n_sink=0, seed=4),
+}
+# cpu sample: a slice of the workload small enough for dense S x S attention on host cores
+CPU_SAMPLE = dict(S=4096, H=2)
+
+
+def cfg3_lengths(total: int):
+    """Lengths uniform in [256, 16384] from seed 2, last one truncated to hit `total` exactly."""
+    g = torch.Generator().manual_seed(2)
+    lens, acc = [], 0
+    while acc < total:
+        L = int(torch.randint(256, 16385, (1,), generator=g))
+        L = min(L, total - acc)
+        lens.append(L)
+        acc += L
+    return lens
+
+
+def visible_pairs(a: int, b: int, W: int, n_sink: int, seq_starts=None) -> int:
+    """Visible (query, key) pairs for queries at global positions [a, b) of one sequence starting at 0."""
+    total = 0
+    # closed form per piece: query p sees min(p, W) + 1 keys, plus sinks out of the window's reach
+    lo = min(b, max(a, W))
+    if lo > a:  # p in [a, lo): p + 1 keys
+        total += (a + 1 + lo) * (lo - a) // 2
+    if b > lo:
+        total += (b - lo) * (W + 1)
+    if n_sink:
+        first = max(a, W + 1)          # p - W > 0: sink 0 out of reach
+        for s in range(n_sink):
+            f = max(a, W + 1 + s)
+            if b > f:
+                total += b - f
+    return total
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, n_gpus):
+        self.n = n_gpus
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons, power = [], [], set(), []
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 8 or not f[0].isdigit() or int(f[0]) >= self.n:
+                continue
+            try:
+                sm.append(float(f[1])), smax.append(float(f[2])), power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["hbm_gbs"]), "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+def cpu_pass(sample, W, n_sink, seed):
+    """One dense fwd+bwd of the oracle on the CPU slice; returns seconds."""
+    from oracle.dense_attn import dense_attn_fwd_bwd
+    g = torch.Generator().manual_seed(seed)
+    S, H = sample["S"], sample["H"]
+    q, k, v, do = (torch.randn(1, S, H, D, generator=g).bfloat16().float() for _ in range(4))
+    t0 = time.perf_counter()
+    dense_attn_fwd_bwd(q, k, v, do, W, None, n_sink)
+    return time.perf_counter() - t0
+
+
+def cpu_tokens_per_s(seconds, sample, wl):
+    # the slice covers S tokens of H of the workload's Hq heads: scale to whole-token throughput
+    return sample["S"] * (sample["H"] / wl["Hq"]) / seconds
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(args.warmup):
+        cpu_pass(CPU_SAMPLE, wl["W"], wl["n_sink"], wl["seed"])
+    times = [cpu_pass(CPU_SAMPLE, wl["W"], wl["n_sink"], wl["seed"]) for _ in range(args.steps)]
+    total = sum(times)
+    val = cpu_tokens_per_s(total / len(times), CPU_SAMPLE, wl)
+    sample = (f"dense torch fp32 fwd+bwd of a 1 x {CPU_SAMPLE['S']} x {CPU_SAMPLE['H']}-head slice per step "
+              f"(of {wl['Hq']} heads), tokens scaled by the head fraction")
+    line = {
+        "impl": "reference", "metric": "ring SWA fwd+bwd tokens/s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, wl, args.gpus),
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, wl, n):
+    s_rank = wl["S"] if args.scaling == "weak" else wl["S"] // n
+    return {"workload": f"{args.workload}: {wl['fn']} B={wl['B']} S_global={s_rank * n} S_per_gpu={s_rank} "
+                        f"Hq={wl['Hq']} Hkv={wl['Hkv']} D={D} window={wl['W']} n_sink={wl['n_sink']} fwd+bwd",
+            "seed": wl["seed"], "cp_size": n, "l2": "inputs larger than L2 (no flush needed)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    wl = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference(args, wl)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torch.distributed.run with --nproc-per-node {args.gpus}")
+    n = world
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    group = None
+    if n > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+
+    import ring_swa
+    from ring_swa import _C
+    from ring_swa import _kernels as K
+
+    fn = getattr(ring_swa, wl["fn"])
+    varlen = "varlen" in wl["fn"]
+    S = wl["S"] if args.scaling == "weak" else wl["S"] // n      # tokens per rank
+    S_g = S * n
+    B, Hq, Hkv, W, n_sink = wl["B"], wl["Hq"], wl["Hkv"], wl["W"], wl["n_sink"]
+    lead = (S,) if varlen else (B, S)
+    g = torch.Generator(device=dev).manual_seed(wl["seed"] * 1000 + rank)
+    q, k, v, do = (torch.randn(*lead, h, D, device=dev, generator=g).bfloat16() for h in (Hq, Hkv, Hkv, Hq))
+    kw = dict(window_size=W)
+    if n > 1:
+        kw.update(cp_group=group, cp_size=n, cp_local_rank=rank)
+    seq_lens = [S_g] * B
+    if varlen:
+        seq_lens = cfg3_lengths(S_g)
+        cu = [0]
+        for L in seq_lens:
+            cu.append(cu[-1] + L)
+        kw.update(cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=dev), cp_size=n)
+    if n_sink and n_sink != 1:
+        kw["num_sink_tokens"] = n_sink
+
+    def step(qq, kk, vv, dd):
+        qq.requires_grad_(True), kk.requires_grad_(True), vv.requires_grad_(True)
+        out = fn(qq, kk, vv, **kw)
+        out.backward(dd)
+        grads = (qq.grad, kk.grad, vv.grad)
+        qq.grad = kk.grad = vv.grad = None
+        return out.detach(), grads
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if n > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(q, k, v, do)
+    sync_all()
+    K.check_device_status(dev)
+
+    # ---------------------------------------------------------------- device-resident timing
+    sampler = ClockSampler(n) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    K.fwd_events, K.bwd_main_events = [], []
+    launches0 = K.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
+        step(q, k, v, do)
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1)
+    launches = K.launch_count - launches0
+    lib = _C.lib()
+    fwd_ms = sum(lib.rswa_event_elapsed_ms(a, b) for a, b in K.fwd_events) / args.steps
+    bwd_ms = sum(lib.rswa_event_elapsed_ms(a, b) for a, b in K.bwd_main_events) / args.steps
+    for a, b in K.fwd_events + K.bwd_main_events:
+        lib.rswa_event_destroy(a), lib.rswa_event_destroy(b)
+    K.fwd_events = K.bwd_main_events = None
+    K.check_device_status(dev)
+
+    # ---------------------------------------------------------------- end to end (host buffers)
+    e2e = None
+    if not args.no_e2e:
+        host_in = [x.detach().cpu().pin_memory() for x in (q, k, v, do)]
+        host_out = [torch.empty_like(x, device="cpu").pin_memory() for x in (q, q, k, v)]
+        dev_in = [torch.empty_like(x) for x in (q, k, v, do)]
+        h2d = sum(x.numel() * x.element_size() for x in host_in)
+        d2h = sum(x.numel() * x.element_size() for x in host_out)
+
+        def e2e_step():
+            for d_, h_ in zip(dev_in, host_in):
+                d_.copy_(h_, non_blocking=True)
+            out, grads = step(dev_in[0].detach(), dev_in[1].detach(), dev_in[2].detach(), dev_in[3])
+            for h_, d_ in zip(host_out, (out,) + grads):
+                h_.copy_(d_, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        sync_all()
+        n_e2e = max(3, min(args.steps, 10))
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        f1.record()
+        sync_all()
+        e2e_ms = f0.elapsed_time(f1) / n_e2e
+    clocks = sampler.stop() if sampler else None
+
+    # ---------------------------------------------------------------- reduce over ranks
+    stats = torch.tensor([ms, fwd_ms, bwd_ms, e2e_ms if not args.no_e2e else 0.0], device=dev, dtype=torch.float64)
+    if n > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms, fwd_ms, bwd_ms, e2e_ms = stats.tolist()
+
+    if rank == 0:
+        tokens = B * S_g
+        ms_step = ms / args.steps
+        peak_tf, peak_gbs, peak_kind = measured_peaks()
+        if varlen:
+            from oracle.dense_attn import in_window_pairs
+            pairs_total = in_window_pairs(seq_lens, W, n_sink)
+        else:
+            pairs_total = B * visible_pairs(0, S_g, W, n_sink)
+        # work is near-uniform over ranks except the first ones; the slowest rank is the last
+        pairs_rank = B * visible_pairs(S_g - S, S_g, W, n_sink) if not varlen else pairs_total / n
+        flops_bwd = 10 * D * Hq * pairs_rank
+        flops_fwd = 4 * D * Hq * pairs_rank
+        ach_bwd = flops_bwd / (bwd_ms * 1e-3) / 1e12
+        ach_fwd = flops_fwd / (fwd_ms * 1e-3) / 1e12
+        line = {
+            "metric": "ring SWA fwd+bwd tokens/s", "value": tokens / (ms_step * 1e-3), "unit": "tokens/s",
+            "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(args, wl, n),
+            "tflops_per_gpu_in_window": 14 * D * Hq * pairs_total / n / (ms_step * 1e-3) / 1e12,
+            "frac_of_bf16_peak": 14 * D * Hq * pairs_total / n / (ms_step * 1e-3) / 1e12 / peak_tf,
+            "roofline": {"kernel": "rswa_bwd_kernel", "bound": "tensor", "achieved": ach_bwd, "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": ach_bwd / peak_tf, "traffic": None,
+                         "peak_source": f"{peak_kind} bf16_tflops (burst)", "ms_per_launch": bwd_ms,
+                         "algorithmic_flops_per_launch": flops_bwd},
+            "roofline_fwd": {"kernel": "rswa_fwd_kernel", "bound": "tensor", "achieved": ach_fwd, "peak": peak_tf,
+                             "unit": "TFLOP/s", "frac": ach_fwd / peak_tf, "ms_per_launch": fwd_ms},
+            "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        if not args.no_e2e:
+            line["e2e"] = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d * n,
+                           "d2h_bytes_per_step": d2h * n, "ms_per_step": e2e_ms}
+        if n == 1 and not args.no_cpu_baseline:
+            t = [cpu_pass(CPU_SAMPLE, W, n_sink, wl["seed"])]          # first call warms torch up
+            t0 = time.perf_counter()
+            runs = []
+            while time.perf_counter() - t0 < 10.0 or len(runs) < 2:
+                runs.append(cpu_pass(CPU_SAMPLE, W, n_sink, wl["seed"]))
+            line["cpu_baseline"] = {
+                "value": cpu_tokens_per_s(statistics.median(runs), CPU_SAMPLE, wl), "unit": "tokens/s",
+                "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"{len(runs)} dense fp32 fwd+bwd passes over a 1 x {CPU_SAMPLE['S']} x {CPU_SAMPLE['H']}-head "
+                          f"slice (of {Hq} heads), median; tokens scaled by the head fraction"}
+        print(json.dumps(line), flush=True)
+    if n > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -9,7 +9,7 @@
  * What each entry point replaces in the reference (paths are inside the reference project):
  * the reference reaches its arithmetic through four Python wrappers around the flash-attn
  * custom ops and one Triton merge kernel; the entry points below are what a maintainer binds
- * instead (with ctypes).
+ * instead (from Python with ctypes, as ring_swa/_C.py does).
  */
 #ifndef RSWA_H_
 #define RSWA_H_
@@ -31,7 +31,6 @@ extern "C" {
 #define RSWA_E_ARG (-1)      /* bad shape / stride / alignment / null pointer */
 #define RSWA_E_UNSUPPORTED (-2)
 #define RSWA_E_CUDA (-3)     /* a CUDA runtime/driver call failed at launch time */
-#define RSWA_E_NOALLOC_SIZE (-4)
 
 /* bits of rswa_bwd_params_t.flags */
 #define RSWA_BWD_INIT 1   /* compute delta = rowsum(dO*O) and zero the fp32 dQ accumulator */
@@ -114,6 +113,11 @@ typedef struct rswa_bwd_params {
   int64_t workspace_bytes;
   int32_t flags;
   int32_t* status;
+  /* Optional profiling hooks: events from rswa_event_create(), recorded on the stream right
+   * before and right after the main backward kernel (the delta and convert kernels excluded).
+   * NULL to skip. */
+  void* ev_main_start;
+  void* ev_main_stop;
 } rswa_bwd_params_t;
 
 int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_t n_q_heads, int32_t head_dim);
@@ -163,6 +167,15 @@ int rswa_cast_from_f32(void* dst, int64_t dst_stride_b, const float* src, int64_
  * No counterpart in the reference. */
 int rswa_selftest_mma(int32_t mode, const void* a, const void* b, float* d, int32_t* status,
                       void* stream);
+
+/* Timing events for benchmarks (thin wrappers of cudaEvent_t so that callers need no CUDA headers).
+ * No counterpart in the reference, which times with torch.cuda.Event
+ * (test/test_ring_swa_nonvarlen.py:295-320). */
+void* rswa_event_create(void);
+void rswa_event_destroy(void* ev);
+int rswa_event_record(void* ev, void* stream);
+/* milliseconds between two recorded events, after synchronising on `stop`; negative on error */
+float rswa_event_elapsed_ms(void* start, void* stop);
 
 int rswa_abi_version(void);
 const char* rswa_last_error(void);

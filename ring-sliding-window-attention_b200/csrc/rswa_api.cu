@@ -306,13 +306,41 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
     rc = launch_delta(*p, delta, q_len_pad, stream);
     if (rc) return rc;
   }
+  if (p->ev_main_start) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream);
   if (total_tiles > 0) {
     rc = launch_bwd(kp, g.dtype, total_tiles, stream);
     if (rc) return rc;
   }
+  if (p->ev_main_stop) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_stop), stream);
   if (p->flags & RSWA_BWD_FINISH) {
     rc = launch_dq_convert(*p, dq_acc, stream);
     if (rc) return rc;
   }
   return RSWA_OK;
+}
+
+extern "C" void* rswa_event_create(void) {
+  cudaEvent_t ev = nullptr;
+  if (cudaEventCreate(&ev) != cudaSuccess) {
+    set_error("rswa_event_create: cudaEventCreate failed");
+    return nullptr;
+  }
+  return ev;
+}
+extern "C" void rswa_event_destroy(void* ev) {
+  if (ev) cudaEventDestroy(static_cast<cudaEvent_t>(ev));
+}
+extern "C" int rswa_event_record(void* ev, void* stream) {
+  if (!ev || cudaEventRecord(static_cast<cudaEvent_t>(ev), static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    set_error("rswa_event_record failed");
+    return RSWA_E_CUDA;
+  }
+  return RSWA_OK;
+}
+extern "C" float rswa_event_elapsed_ms(void* start, void* stop) {
+  float ms = -1.f;
+  if (!start || !stop) return -1.f;
+  if (cudaEventSynchronize(static_cast<cudaEvent_t>(stop)) != cudaSuccess) return -1.f;
+  if (cudaEventElapsedTime(&ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)) != cudaSuccess) return -1.f;
+  return ms;
 }

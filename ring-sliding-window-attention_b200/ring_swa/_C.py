@@ -59,6 +59,7 @@ class BwdParams(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("flags", C.c_int32),
         ("status", C.c_void_p),
+        ("ev_main_start", C.c_void_p), ("ev_main_stop", C.c_void_p),
     ]
 
 
@@ -87,6 +88,10 @@ SYMBOLS = {
                                        C.c_int64, C.c_void_p]),
     "rswa_cast_from_f32": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                      C.c_int64, C.c_void_p]),
+    "rswa_event_create": (C.c_void_p, []),
+    "rswa_event_destroy": (None, [C.c_void_p]),
+    "rswa_event_record": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "rswa_event_elapsed_ms": (C.c_float, [C.c_void_p, C.c_void_p]),
     "rswa_selftest_mma": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 
@@ -118,6 +123,6 @@ def check(rc: int, what: str) -> None:
     if rc == 0:
         return
     msg = lib().rswa_last_error().decode("utf-8", "replace")
-    if rc in (-1, -2, -4):
+    if rc in (-1, -2):
         raise ValueError(f"{what}: {msg}")
     raise RuntimeError(f"{what}: {msg} (code {rc})")

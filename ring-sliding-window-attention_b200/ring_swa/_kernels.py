@@ -32,6 +32,15 @@ class KVSpan:
 
 _status = {}
 
+# Number of kernels of this library launched so far (benchmarks report the count per timed region).
+launch_count = 0
+
+# When set to a list, every main backward kernel is bracketed by a fresh pair of timing events which
+# is appended here as (start, stop) raw handles; benchmarks read them with rswa_event_elapsed_ms.
+bwd_main_events = None
+# Same for the forward kernel (one launch per rswa_fwd call).
+fwd_events = None
+
 
 def status_word(device: torch.device) -> torch.Tensor:
     """Device word the kernels raise when a bounded device-side wait runs out."""
@@ -144,7 +153,15 @@ def fwd(q: torch.Tensor, spans: Sequence[KVSpan], window: int, n_sink: int, scal
     if q_tiles is not None and q_tiles[1] <= q_tiles[0]:
         return out, lse
     p.status = status_word(q.device).data_ptr()
+    if fwd_events is not None:
+        e0, e1 = _C.lib().rswa_event_create(), _C.lib().rswa_event_create()
+        fwd_events.append((e0, e1))
+        _C.lib().rswa_event_record(e0, _stream())
     _C.check(_C.lib().rswa_fwd(C.byref(p), _stream()), "rswa_fwd")
+    if fwd_events is not None:
+        _C.lib().rswa_event_record(e1, _stream())
+    global launch_count
+    launch_count += 1
     return out, lse
 
 
@@ -185,7 +202,12 @@ def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.
     p.workspace_bytes = workspace.numel()
     p.flags = int(flags)
     p.status = status_word(q.device).data_ptr()
+    if bwd_main_events is not None:
+        p.ev_main_start, p.ev_main_stop = _C.lib().rswa_event_create(), _C.lib().rswa_event_create()
+        bwd_main_events.append((p.ev_main_start, p.ev_main_stop))
     _C.check(_C.lib().rswa_bwd(C.byref(p), _stream()), "rswa_bwd")
+    global launch_count
+    launch_count += (1 if flags & _C.BWD_INIT else 0) + (1 if spans else 0) + (1 if flags & _C.BWD_FINISH else 0)
     return workspace
 
 
@@ -211,6 +233,8 @@ def merge(o_a: torch.Tensor, lse_a: torch.Tensor, o_b: torch.Tensor, lse_b: torc
     p.lse_a, p.lse_b, p.lse = lse_a.data_ptr(), lse_b.data_ptr(), lse_out.data_ptr()
     p.lse_stride_b, p.lse_stride_h = lse_a.stride(0), lse_a.stride(1)
     _C.check(_C.lib().rswa_merge(C.byref(p), _stream()), "rswa_merge")
+    global launch_count
+    launch_count += 1
     return out, lse_out
 
 
@@ -230,6 +254,8 @@ def halo_accumulate(acc: torch.Tensor, recv: torch.Tensor) -> None:
     code = _C.DTYPE_F32 if recv.dtype == torch.float32 else _dtype_code(recv)
     _C.check(_C.lib().rswa_halo_accumulate(acc.data_ptr(), asb, recv.data_ptr(), rsb, code, B, n, _stream()),
              "rswa_halo_accumulate")
+    global launch_count
+    launch_count += 1
 
 
 def cast_from_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
@@ -239,6 +265,8 @@ def cast_from_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
     _, ssb, _ = _rows(src)
     _C.check(_C.lib().rswa_cast_from_f32(dst.data_ptr(), dsb, src.data_ptr(), ssb, _dtype_code(dst), B, n,
                                          _stream()), "rswa_cast_from_f32")
+    global launch_count
+    launch_count += 1
 
 
 def selftest_mma(mode: int, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,152 @@
+"""The four public functions on one GPU (cp_group=None): parity with the oracle, with the vectors the
+reference's ring functions produced (tests/golden/ref_ring_d128_*.npz), and the reference's error
+behaviour.  Full-size checks use properties that do not need a dense oracle."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close, assert_lse_close, randn_bf16
+from oracle.dense_attn import dense_attn_fwd_bwd
+from ring_cases import GOLDEN, case_params, make_inputs
+
+pytestmark = pytest.mark.gpu
+D = 128
+
+
+def _run(fn, q, k, v, do, **kw):
+    dev = torch.device("cuda")
+    ql, kl, vl = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+    out = fn(ql, kl, vl, **kw)
+    out.backward(do.to(dev))
+    from ring_swa._kernels import check_device_status
+    check_device_status()
+    return out.detach(), ql.grad, kl.grad, vl.grad
+
+
+def test_sliding_window_nonvarlen():
+    import ring_swa
+    q, k, v, do = (randn_bf16(2, 500, h, D, seed=s) for h, s in ((4, 1), (2, 2), (2, 3), (4, 4)))
+    ro, _, rdq, rdk, rdv = dense_attn_fwd_bwd(q, k, v, do, 120)
+    out, dq, dk, dv = _run(ring_swa.ring_sliding_window_attn, q, k, v, do, window_size=120)
+    for n, a, b in (("out", out, ro), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        assert_close(n, a, b)
+    assert out.dtype == torch.bfloat16 and out.shape == q.shape
+
+
+def test_streaming_llm_nonvarlen_and_naive_alias():
+    import ring_swa
+    from ring_swa.streaming_llm.naive import naive_streaming_llm_attn
+    q, k, v, do = (randn_bf16(1, 700, h, D, seed=s) for h, s in ((4, 5), (1, 6), (1, 7), (4, 8)))
+    ro, _, rdq, rdk, rdv = dense_attn_fwd_bwd(q, k, v, do, 64, None, 1)
+    out, dq, dk, dv = _run(ring_swa.ring_streaming_llm_attn, q, k, v, do, window_size=64, softmax_scale=None)
+    for n, a, b in (("out", out, ro), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        assert_close(n, a, b)
+    out2, *_ = _run(naive_streaming_llm_attn, q, k, v, do, window_size=64)
+    assert torch.equal(out, out2)
+    ro4, *_ = dense_attn_fwd_bwd(q, k, v, do, 64, None, 4)
+    out4, *_ = _run(ring_swa.ring_streaming_llm_attn, q, k, v, do, window_size=64, num_sink_tokens=4)
+    assert_close("out(4 sinks)", out4, ro4)
+
+
+def test_varlen_functions():
+    import ring_swa
+    cu = [0, 100, 101, 400, 777]
+    q, k, v, do = (randn_bf16(777, h, D, seed=s) for h, s in ((4, 9), (2, 10), (2, 11), (4, 12)))
+    cud = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    for fn, ns in ((ring_swa.ring_sliding_window_attn_varlen, 0), (ring_swa.ring_streaming_llm_attn_varlen, 1)):
+        ro, _, rdq, rdk, rdv = dense_attn_fwd_bwd(q[None], k[None], v[None], do[None], 90, 0.1, ns, cu)
+        out, dq, dk, dv = _run(fn, q, k, v, do, window_size=90, cu_seqlens=cud, cp_size=1, softmax_scale=0.1)
+        for n, a, b in (("out", out, ro[0]), ("dq", dq, rdq[0]), ("dk", dk, rdk[0]), ("dv", dv, rdv[0])):
+            assert_close(n, a, b)
+
+
+def test_reference_error_behaviour():
+    import ring_swa
+    dev = "cuda"
+    q = torch.zeros(256, 4, D, dtype=torch.bfloat16, device=dev)
+    cu = torch.tensor([0, 256], dtype=torch.int32, device=dev)
+    # ring_swa/sliding_window/varlen.py:401-403 divides by cp_size before looking at cp_group
+    with pytest.raises(TypeError):
+        ring_swa.ring_sliding_window_attn_varlen(q, q, q, 10, cu)
+    with pytest.raises(AssertionError, match="cu_seqlens does not match"):
+        ring_swa.ring_sliding_window_attn_varlen(q, q, q, 10, cu, cp_size=2)
+    k3 = torch.zeros(256, 3, D, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(AssertionError, match="divisible"):
+        ring_swa.ring_sliding_window_attn_varlen(q, k3, k3, 10, cu, cp_size=1)
+    q4 = torch.zeros(1, 256, 4, D, dtype=torch.bfloat16, device=dev)
+    k4 = torch.zeros(1, 128, 4, D, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(AssertionError, match="Sequence length must be the same"):
+        ring_swa.ring_sliding_window_attn(q4, k4, k4, 10)
+    with pytest.raises(ValueError):
+        ring_swa.ring_sliding_window_attn(q4.float(), q4.float(), q4.float(), 10)
+
+
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLDEN, "ref_ring_d128_*.npz"))),
+                         ids=lambda p: os.path.basename(p)[:-4])
+def test_matches_reference_ring_vectors(path):
+    """Global result of the reference's ring functions (their own code on gloo ranks) vs this
+    implementation on one GPU, same bf16-representable inputs."""
+    import ring_swa
+    z = np.load(path)
+    c = {k: z[k] for k in z.files}
+    p = case_params(c)
+    fn_name = str(c["fn"])
+    varlen = "varlen" in fn_name
+    q, k, v, do = make_inputs(p["seed"], p["T"], p["hq"], p["hkv"], p["d"], True, None if varlen else p["B"],
+                              p["sink_rows"])
+    kw = dict(window_size=p["W"])
+    if varlen:
+        kw.update(cu_seqlens=torch.tensor(p["cu"], dtype=torch.int32, device="cuda"), cp_size=1)
+    out, dq, dk, dv = _run(getattr(ring_swa, fn_name), q.bfloat16(), k.bfloat16(), v.bfloat16(), do.bfloat16(), **kw)
+    for n, a in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv)):
+        assert_close(n, a, torch.from_numpy(c[n].astype(np.float32)))
+
+
+def _torch_block_reference(q, k, v, do, W, n_sink, a, b, heads):
+    """fp32 torch attention on the token range [a - W, b + W) for a few heads, on the GPU: every query
+    in [a, b + W) then has its complete window, so out/dq of queries [a, b) and dk/dv of keys [a, b)
+    equal the full-sequence values (when n_sink == 0)."""
+    lo, hi = max(0, a - W), min(q.shape[1], b + W)
+    g = q.shape[2] // k.shape[2]
+    kh = sorted({h // g for h in heads})
+    assert len(kh) == 1
+    qs = q[:, lo:hi, heads].float().requires_grad_(True)
+    ks = k[:, lo:hi, kh].float().requires_grad_(True)
+    vs = v[:, lo:hi, kh].float().requires_grad_(True)
+    n = hi - lo
+    i = torch.arange(n, device=q.device)
+    mask = (i[None, :] <= i[:, None]) & (i[:, None] - i[None, :] <= W)
+    s = torch.einsum("bihd,bjd->bhij", qs, ks[:, :, 0]) * (D ** -0.5)
+    s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    o = torch.einsum("bhij,bjd->bihd", torch.softmax(s, -1), vs[:, :, 0])
+    o.backward(do[:, lo:hi, heads].float())
+    sl = slice(a - lo, b - lo)
+    return o.detach()[:, sl], lse[:, :, sl], qs.grad[:, sl], ks.grad[:, sl], vs.grad[:, sl]
+
+
+def test_full_size_config_spot_blocks():
+    """BASELINE configuration 2 at full size on one GPU (B=2, S=32768, 32/32 heads, W=1000): blocks of
+    the result are compared with an fp32 torch computation of the same tokens, plus run-to-run
+    agreement of the forward."""
+    import ring_swa
+    dev = torch.device("cuda")
+    B, S, H, W = 2, 32768, 32, 1000
+    g = torch.Generator(device=dev).manual_seed(1)
+    q, k, v, do = (torch.randn(B, S, H, D, device=dev, generator=g).bfloat16() for _ in range(4))
+    q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+    out = ring_swa.ring_sliding_window_attn(q, k, v, W)
+    out.backward(do)
+    out2 = ring_swa.ring_sliding_window_attn(q.detach(), k.detach(), v.detach(), W)
+    from ring_swa._kernels import check_device_status
+    check_device_status()
+    assert torch.equal(out, out2)
+    for a, b, heads in ((0, 300, [0]), (5000, 5300, [7]), (32468, 32768, [31]), (16300, 16500, [16])):
+        ro, _rl, rdq, rdk, rdv = _torch_block_reference(q.detach(), k.detach(), v.detach(), do, W, 0, a, b, heads)
+        assert_close(f"out[{a}:{b}]", out.detach()[:, a:b, heads], ro)
+        assert_close(f"dq[{a}:{b}]", q.grad[:, a:b, heads], rdq)
+        assert_close(f"dk[{a}:{b}]", k.grad[:, a:b, heads], rdk)
+        assert_close(f"dv[{a}:{b}]", v.grad[:, a:b, heads], rdv)
