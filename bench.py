@@ -43,6 +43,8 @@ WORKLOADS = {
     "cfg3": dict(fn="ring_sliding_window_attn_varlen", B=1, S=65536, Hq=32, Hkv=8, W=4096, n_sink=0, seed=2),
     "cfg4": dict(fn="ring_streaming_llm_attn", B=1, S=131072, Hq=32, Hkv=8, W=8192, n_sink=1, seed=3),
     "cfg5": dict(fn="ring_sliding_window_attn", B=1, S=262144, Hq=64, Hkv=8, W=65536, n_sink=0, seed=4),
+    # reduced case for profiler captures: same kernels, inputs still larger than L2, < 1 GB on the device
+    "small": dict(fn="ring_sliding_window_attn", B=1, S=16384, Hq=16, Hkv=16, W=1000, n_sink=0, seed=1),
 }
 # cpu sample: a slice of the workload small enough for dense S x S attention on host cores
 CPU_SAMPLE = dict(S=4096, H=2)

@@ -48,13 +48,15 @@ class RingCtx:
         return dist.get_global_rank(self.group, group_rank)
 
 
-def _exchange(ops: List[dist.P2POp]):
-    return dist.batch_isend_irecv(ops) if ops else []
+def _exchange(ops: List[dist.P2POp]) -> list:
+    return list(dist.batch_isend_irecv(ops)) if ops else []
 
 
 def _wait(works) -> None:
-    for w in works:
-        w.wait()
+    """Waits for every request once and empties the list (a second wait on a finished gloo
+    send/recv request blocks for ever, so the call must be idempotent)."""
+    while works:
+        works.pop().wait()
 
 
 def _dense(t: torch.Tensor) -> torch.Tensor:

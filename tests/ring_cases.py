@@ -58,7 +58,9 @@ def run_rank(rank, ws, port, jobs, outdir, device="cpu"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.set_num_threads(1)
-    dist.init_process_group("gloo" if device == "cpu" else "nccl", rank=rank, world_size=ws)
+    from datetime import timedelta
+    dist.init_process_group("gloo" if device == "cpu" else "nccl", rank=rank, world_size=ws,
+                            timeout=timedelta(seconds=180))
     import ring_swa
     if device == "cpu":
         import cpu_backend

@@ -33,6 +33,7 @@ def _assert_small(results, jobs, tol):
                     f"rank {r} {job['fn']} W={job['W']} cu={job.get('cu')} {name}: {errs}")
 
 
+@pytest.mark.timeout(900)
 def test_ring_matches_reference_pins_cp4():
     jobs = []
     for c in load_pins():
@@ -59,6 +60,7 @@ def _dense_job(fn, T, B, hq, hkv, d, W, seed, cu=None, n_sink=0):
                 expect={k_: v_.float().numpy() for k_, v_ in exp.items()})
 
 
+@pytest.mark.timeout(600)
 def test_ring_matches_dense_oracle_cp2():
     jobs = [
         # phase split: tiles [1,3) local only, tile 0 with halo
