@@ -31,6 +31,10 @@ extern "C" {
 #define RSWA_E_ARG (-1)      /* bad shape / stride / alignment / null pointer */
 #define RSWA_E_UNSUPPORTED (-2)
 #define RSWA_E_CUDA (-3)     /* a CUDA runtime/driver call failed at launch time */
+#define RSWA_E_NOALLOC_SIZE (-4) /* rswa_bwd_noalloc: the problem does not fit the built-in scratch */
+
+/* size of the scratch array inside the library that rswa_bwd_noalloc works in */
+#define RSWA_NOALLOC_SCRATCH_BYTES (64ll << 20)
 
 /* bits of rswa_bwd_params_t.flags */
 #define RSWA_BWD_INIT 1   /* compute delta = rowsum(dO*O) and zero the fp32 dQ accumulator */
@@ -122,6 +126,26 @@ typedef struct rswa_bwd_params {
 
 int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_t n_q_heads, int32_t head_dim);
 int rswa_bwd(const rswa_bwd_params_t* p, void* stream);
+
+/* The whole backward for callers that cannot allocate device memory: same inputs, outputs and
+ * result as rswa_bwd with flags INIT|FINISH, but `workspace`, `workspace_bytes` and `flags` are
+ * ignored.  The scratch (fp32 dQ accumulator + delta rows) is a fixed array of
+ * RSWA_NOALLOC_SCRATCH_BYTES that is part of the library's device image, so every GPU that loads
+ * the library carries it until the process exits, and the call itself never allocates or frees.
+ * Meant for hosts that are handed only the operator's tensors (a plugin inside another runtime),
+ * that gave away all device memory at start-up, or that must not stall their other streams with
+ * the device-wide synchronisation an allocation implies.
+ *  - rswa_bwd_workspace_bytes(batch, q_len, n_q_heads, 128) must not exceed
+ *    RSWA_NOALLOC_SCRATCH_BYTES (about batch*q_len*n_q_heads <= 130000 rows, e.g. 4096 tokens of
+ *    32 heads); larger problems return RSWA_E_NOALLOC_SIZE and launch nothing.
+ *  - The first call on each device looks the array's device address up (with that device
+ *    current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the array: it is re-initialised at the start of each call, and
+ *    two calls that can overlap on the GPU (different streams, no dependency) corrupt each other.
+ * Has no counterpart in the reference, whose backward allocates its accumulators with torch on
+ * every call (ring_swa/sliding_window/nonvarlen.py:192-195). */
+int rswa_bwd_noalloc(const rswa_bwd_params_t* p, void* stream);
+int64_t rswa_noalloc_scratch_bytes(void);
 
 /* Log-sum-exp merge of two partial results over the same queries:
  *   lse = log(exp(lse_a) + exp(lse_b)),  o = o_a*exp(lse_a-lse) + o_b*exp(lse_b-lse)

@@ -83,6 +83,8 @@ SYMBOLS = {
     "rswa_fwd": (C.c_int, [C.POINTER(FwdParams), C.c_void_p]),
     "rswa_bwd_workspace_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "rswa_bwd": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
+    "rswa_bwd_noalloc": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
+    "rswa_noalloc_scratch_bytes": (C.c_int64, []),
     "rswa_merge": (C.c_int, [C.POINTER(MergeParams), C.c_void_p]),
     "rswa_halo_accumulate": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                        C.c_int64, C.c_void_p]),
@@ -123,6 +125,6 @@ def check(rc: int, what: str) -> None:
     if rc == 0:
         return
     msg = lib().rswa_last_error().decode("utf-8", "replace")
-    if rc in (-1, -2):
+    if rc in (-1, -2, -4):
         raise ValueError(f"{what}: {msg}")
     raise RuntimeError(f"{what}: {msg} (code {rc})")

@@ -211,6 +211,40 @@ def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.
     return workspace
 
 
+def bwd_noalloc(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.Tensor,
+                dout: torch.Tensor, dq: torch.Tensor, window: int, n_sink: int, scale: float,
+                q_pos_start: int = 0, cu_seqlens: Optional[torch.Tensor] = None) -> None:
+    """A whole backward through rswa_bwd_noalloc: no workspace tensor is created or passed.
+
+    For integrations that may not allocate device memory where they call the backward (they only
+    hold the operator's own tensors, or allocation is forbidden after start-up): the scratch is
+    the fixed 64 MiB array inside librswa.so.  Raises ValueError when the problem is too large
+    for it.  Calls on one device share that array, so they must not overlap on the GPU.
+    """
+    for name, t in (("q", q), ("out", out), ("dout", dout), ("dq", dq)):
+        _check4(name, t)
+        if t.dtype != q.dtype or t.shape != q.shape:
+            raise ValueError(f"{name} must match q in dtype and shape")
+    if lse.dtype != torch.float32 or lse.stride(2) != 1:
+        raise ValueError("lse must be float32 [B, Hq, S] with contiguous tokens")
+    p = _C.BwdParams()
+    _fill_geom(p.g, q, spans, window, n_sink, scale, q_pos_start, cu_seqlens, grads=True)
+    p.q = q.data_ptr()
+    p.q_stride_b, p.q_stride_t, p.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
+    p.out = out.data_ptr()
+    p.o_stride_b, p.o_stride_t, p.o_stride_h = out.stride(0), out.stride(1), out.stride(2)
+    p.dout = dout.data_ptr()
+    p.do_stride_b, p.do_stride_t, p.do_stride_h = dout.stride(0), dout.stride(1), dout.stride(2)
+    p.lse = lse.data_ptr()
+    p.lse_stride_b, p.lse_stride_h = lse.stride(0), lse.stride(1)
+    p.dq = dq.data_ptr()
+    p.dq_stride_b, p.dq_stride_t, p.dq_stride_h = dq.stride(0), dq.stride(1), dq.stride(2)
+    p.status = status_word(q.device).data_ptr()
+    _C.check(_C.lib().rswa_bwd_noalloc(C.byref(p), _stream()), "rswa_bwd_noalloc")
+    global launch_count
+    launch_count += 2 + (1 if spans else 0)
+
+
 def merge(o_a: torch.Tensor, lse_a: torch.Tensor, o_b: torch.Tensor, lse_b: torch.Tensor,
           out: Optional[torch.Tensor] = None, lse_out: Optional[torch.Tensor] = None
           ) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -1,0 +1,63 @@
+"""rswa_bwd_noalloc, the backward for hosts that cannot allocate device memory at the call site (they
+are given the operator's tensors and nothing else, or allocation is off limits once the process has
+started serving).  Called through the C ABI and compared with rswa_bwd on the same inputs, twice in a
+row: the second call works in the same built-in scratch array and must not see the first call's sums.
+
+This file sorts last on purpose, so that a run stopping at the first failure has run everything else.
+"""
+import pytest
+import torch
+
+from gpu_util import assert_close, randn_bf16
+
+pytestmark = pytest.mark.gpu
+D = 128
+
+
+def _problem(seed, S, Hq, Hkv, W, n_sink, cu):
+    from ring_swa import _kernels as K
+    dev = torch.device("cuda")
+    q = randn_bf16(1, S, Hq, D, seed=seed).to(dev)
+    k = randn_bf16(1, S, Hkv, D, seed=seed + 1).to(dev)
+    v = randn_bf16(1, S, Hkv, D, seed=seed + 2).to(dev)
+    do = randn_bf16(1, S, Hq, D, seed=seed + 3).to(dev)
+    cud = torch.tensor(cu, dtype=torch.int32, device=dev) if cu else None
+    out, lse = K.fwd(q, [K.KVSpan(k, v, 0)], W, n_sink, D ** -0.5, 0, cud)
+    return q, k, v, do, out, lse, cud
+
+
+def _both(seed, S, Hq, Hkv, W, n_sink, cu):
+    from ring_swa import _kernels as K
+    q, k, v, do, out, lse, cud = _problem(seed, S, Hq, Hkv, W, n_sink, cu)
+    ref = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    K.bwd(q, [K.KVSpan(k, v, 0, dk=ref[1], dv=ref[2])], out, lse, do, ref[0], W, n_sink, D ** -0.5, 0, cud)
+    got = [torch.full_like(q, float("nan")), torch.full_like(k, float("nan")), torch.full_like(v, float("nan"))]
+    before = torch.cuda.memory_allocated()
+    K.bwd_noalloc(q, [K.KVSpan(k, v, 0, dk=got[1], dv=got[2])], out, lse, do, got[0], W, n_sink, D ** -0.5, 0, cud)
+    assert torch.cuda.memory_allocated() == before      # nothing came from torch's allocator either
+    K.check_device_status()
+    for name, a, b in zip(("dq", "dk", "dv"), got, ref):
+        assert_close(name, a, b.float())
+
+
+def test_noalloc_backward_matches_twice_in_a_row():
+    # first call: large values left behind in the shared scratch ...
+    _both(seed=100, S=900, Hq=8, Hkv=2, W=200, n_sink=1, cu=None)
+    # ... second call: another shape, packed sequences; must start from a clean accumulator
+    _both(seed=200, S=515, Hq=4, Hkv=4, W=64, n_sink=0, cu=[0, 100, 101, 515])
+    # and the same problem again
+    _both(seed=200, S=515, Hq=4, Hkv=4, W=64, n_sink=0, cu=[0, 100, 101, 515])
+
+
+def test_noalloc_rejects_what_does_not_fit():
+    from ring_swa import _C
+    from ring_swa import _kernels as K
+    dev = torch.device("cuda")
+    assert _C.lib().rswa_noalloc_scratch_bytes() == 64 << 20
+    S, H = 8192, 32                      # 262144 rows: 128 MiB of fp32 dQ, twice the built-in array
+    q = torch.zeros(1, S, H, D, dtype=torch.bfloat16, device=dev)
+    lse = torch.zeros(1, H, S, dtype=torch.float32, device=dev)
+    dk = torch.zeros_like(q)
+    with pytest.raises(ValueError, match="scratch"):
+        K.bwd_noalloc(q, [K.KVSpan(q, q, 0, dk=dk, dv=dk)], q, lse, q, torch.empty_like(q), 100, 0, 0.1)
+    K.check_device_status()
