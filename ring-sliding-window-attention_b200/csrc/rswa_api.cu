@@ -9,7 +9,7 @@ namespace rswa {
 
 int launch_fwd(const FwdKernelParams& kp, int dtype, cudaStream_t stream);
 int launch_bwd(const BwdKernelParams& kp, int dtype, int total_key_tiles, cudaStream_t stream);
-int launch_delta(const rswa_bwd_params_t& p, float* delta, int q_len_pad, cudaStream_t stream);
+int launch_delta(const rswa_bwd_params_t& p, float* delta, float* lse2, int q_len_pad, cudaStream_t stream);
 int launch_dq_convert(const rswa_bwd_params_t& p, const float* dq_acc, cudaStream_t stream);
 
 static thread_local char g_err[512] = "";
@@ -214,8 +214,8 @@ extern "C" int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_
   if (batch <= 0 || q_len <= 0 || n_q_heads <= 0 || head_dim != kHeadDim) return -1;
   const int64_t q_len_pad = (static_cast<int64_t>(q_len) + kTile - 1) / kTile * kTile;
   const int64_t dq = static_cast<int64_t>(batch) * q_len * n_q_heads * head_dim * 4;
-  const int64_t delta = static_cast<int64_t>(batch) * n_q_heads * q_len_pad * 4;
-  return ((dq + 255) / 256) * 256 + delta;
+  const int64_t rows = static_cast<int64_t>(batch) * n_q_heads * q_len_pad * 4;  // delta, and lse * log2(e)
+  return ((dq + 255) / 256) * 256 + 2 * rows;
 }
 
 extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
@@ -246,6 +246,7 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
   const int64_t dq_bytes = static_cast<int64_t>(g.batch) * g.q_len * g.n_q_heads * kHeadDim * 4;
   float* dq_acc = static_cast<float*>(p->workspace);
   float* delta = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + ((dq_bytes + 255) / 256) * 256);
+  float* lse2 = delta + static_cast<int64_t>(g.batch) * g.n_q_heads * q_len_pad;
 
   BwdKernelParams kp;
   memset(&kp, 0, sizeof(kp));
@@ -288,9 +289,7 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
   kp.scale_log2 = g.softmax_scale * 1.4426950408889634f;
   kp.cu = g.cu_seqlens;
   kp.n_seqs = g.n_seqs;
-  kp.lse = p->lse;
-  kp.l_sb = p->lse_stride_b;
-  kp.l_sh = p->lse_stride_h;
+  kp.lse2 = lse2;
   kp.delta = delta;
   kp.d_sb = static_cast<long long>(g.n_q_heads) * q_len_pad;
   kp.d_sh = q_len_pad;
@@ -303,7 +302,7 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
       set_error("rswa_bwd: memset: %s", cudaGetErrorString(e));
       return RSWA_E_CUDA;
     }
-    rc = launch_delta(*p, delta, q_len_pad, stream);
+    rc = launch_delta(*p, delta, lse2, q_len_pad, stream);
     if (rc) return rc;
   }
   if (p->ev_main_start) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream);

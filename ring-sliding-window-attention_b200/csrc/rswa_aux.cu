@@ -30,27 +30,41 @@ __device__ __forceinline__ uint32_t pack2f(float lo, float hi) {
   }
 }
 
-// One warp per (b, t, h) row of 128 elements: lane handles 4 consecutive elements (8 bytes).
+// Half a warp per (b, t, h) row of 128 elements (16 bytes per lane and tensor).  Writes
+// delta = rowsum(dO * O) and lse2 = lse * log2(e) into rows padded to whole 128-query tiles; the
+// padding gets delta = 0 and lse2 = +inf so that P = exp2(s - lse2) vanishes there.
 template <bool kBf16>
 __global__ void delta_kernel(const uint16_t* __restrict__ out, long long o_sb, long long o_st, long long o_sh,
                              const uint16_t* __restrict__ dout, long long d_sb, long long d_st, long long d_sh,
-                             float* __restrict__ delta, int batch, int q_len, int hq, int q_len_pad) {
-  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const long long n_rows = static_cast<long long>(batch) * q_len * hq;
+                             const float* __restrict__ lse, long long l_sb, long long l_sh,
+                             float* __restrict__ delta, float* __restrict__ lse2, int batch, int q_len, int hq,
+                             int q_len_pad) {
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const int sub = threadIdx.x & 15;
+  const long long n_rows = static_cast<long long>(batch) * q_len_pad * hq;
   if (row >= n_rows) return;
   const int h = row % hq;
   const long long bt = row / hq;
-  const int t = bt % q_len;
-  const int b = bt / q_len;
-  const uint2 a = *reinterpret_cast<const uint2*>(out + b * o_sb + t * o_st + h * o_sh + lane * 4);
-  const uint2 d = *reinterpret_cast<const uint2*>(dout + b * d_sb + t * d_st + h * d_sh + lane * 4);
-  const float2 a0 = unpack2<kBf16>(a.x), a1 = unpack2<kBf16>(a.y);
-  const float2 d0 = unpack2<kBf16>(d.x), d1 = unpack2<kBf16>(d.y);
-  float s = a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y;
+  const int t = bt % q_len_pad;
+  const int b = bt / q_len_pad;
+  float s = 0.f;
+  if (t < q_len) {
+    const uint4 a = *reinterpret_cast<const uint4*>(out + b * o_sb + t * o_st + h * o_sh + sub * 8);
+    const uint4 d = *reinterpret_cast<const uint4*>(dout + b * d_sb + t * d_st + h * d_sh + sub * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (lane == 0) delta[(static_cast<long long>(b) * hq + h) * q_len_pad + t] = s;
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = unpack2<kBf16>(aw[i]), y = unpack2<kBf16>(dw[i]);
+      s += x.x * y.x + x.y * y.y;
+    }
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (sub == 0) {
+    const long long idx = (static_cast<long long>(b) * hq + h) * q_len_pad + t;
+    delta[idx] = s;
+    lse2[idx] = t < q_len ? lse[b * l_sb + h * l_sh + t] * 1.4426950408889634f : INFINITY;
+  }
 }
 
 // dq = scale * dq_acc, fp32 [b, t, h, 128] contiguous -> 16-bit with strides.  8 elements/thread.
@@ -163,16 +177,16 @@ int check_launch(const char* what) {
 
 }  // namespace
 
-int launch_delta(const rswa_bwd_params_t& p, float* delta, int q_len_pad, cudaStream_t stream) {
+int launch_delta(const rswa_bwd_params_t& p, float* delta, float* lse2, int q_len_pad, cudaStream_t stream) {
   const rswa_geom_t& g = p.g;
-  const long long rows = static_cast<long long>(g.batch) * g.q_len * g.n_q_heads;
+  const long long rows = static_cast<long long>(g.batch) * q_len_pad * g.n_q_heads;
   const int threads = 256;
-  const long long blocks = (rows * 32 + threads - 1) / threads;
+  const long long blocks = (rows * 16 + threads - 1) / threads;
   auto kern = g.dtype == RSWA_DTYPE_BF16 ? delta_kernel<true> : delta_kernel<false>;
   kern<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
       static_cast<const uint16_t*>(p.out), p.o_stride_b, p.o_stride_t, p.o_stride_h,
-      static_cast<const uint16_t*>(p.dout), p.do_stride_b, p.do_stride_t, p.do_stride_h, delta, g.batch, g.q_len,
-      g.n_q_heads, q_len_pad);
+      static_cast<const uint16_t*>(p.dout), p.do_stride_b, p.do_stride_t, p.do_stride_h, p.lse, p.lse_stride_b,
+      p.lse_stride_h, delta, lse2, g.batch, g.q_len, g.n_q_heads, q_len_pad);
   return check_launch("rswa_bwd(delta)");
 }
 

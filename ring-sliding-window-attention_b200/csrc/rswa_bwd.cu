@@ -5,18 +5,25 @@
 //
 //   S^T  = K Q^T          A = K   (smem, K-major)     B = Q   (smem, K-major)
 //   dP^T = V dO^T         A = V   (smem, K-major)     B = dO  (smem, K-major)
-//   P^T  = exp2(S^T * scale_log2 - lse),   dS^T = P^T * (dP^T - delta)      (8 warps)
+//   P^T  = exp2(S^T * scale_log2 - lse2),   dS^T = P^T * (dP^T - delta)      (8 compute warps)
 //   dV  += P^T dO         A = P^T (TMEM)              B = dO  (smem, MN-major)
 //   dK  += dS^T Q         A = dS^T(TMEM)              B = Q   (smem, MN-major)
 //   dQ   = dS K           A = dS^T(smem, MN-major)    B = K   (smem, MN-major)
 //
 // dK and dV stay in TMEM for the whole CTA (summed over the query heads of the group) and are
 // written once; dQ tiles are added into an fp32 accumulator in global memory with vector
-// reductions and converted afterwards.  P is recomputed from the saved log-sum-exp, and delta is
-// rowsum(dO * O), which is what makes a per-span backward against the FINAL out/lse exact
-// (the property the reference's per-hop backward relies on, ring_swa/ops/attn.py:63-126).
+// reductions by a dedicated warp group and converted afterwards.  P is recomputed from the saved
+// log-sum-exp, and delta is rowsum(dO * O), which is what makes a per-span backward against the
+// FINAL out/lse exact (the property the reference's per-hop backward relies on,
+// ring_swa/ops/attn.py:63-126).
+//
+// Roles (16 warps): warp 0 TMA producer, warp 1 MMA issuer, warps 4-11 compute, warps 12-15 dQ
+// reduction.  Registers are re-balanced with setmaxnreg (compute warps get 200).
 //
 // TMEM columns: [0,128) dK, [128,256) dV, [256,384) S^T then P^T | dS^T, [384,512) dP^T then dQ.
+// The MMA thread never waits for its own MMAs: tcgen05.mma instructions of one thread execute in
+// issue order, so S^T of the next query tile may be issued right behind the MMAs that still read
+// P^T / dS^T from the same columns.
 #include "rswa_common.cuh"
 #include "tc05.cuh"
 
@@ -25,19 +32,23 @@ using namespace tc05;
 
 namespace {
 
-constexpr int kBwdThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2-9: compute
+constexpr int kBwdThreads = 512;
 constexpr int kBwdTmemCols = 512;
+constexpr int kComputeThreads = 256;
+constexpr int kReduceThreads = 128;
 
 struct BwdCtl {
-  uint64_t kv_full, qdo_full[2], stage_free[2], sdp_ready, pds_ready, mma2_done, dq_done;
+  uint64_t kv_full, qdo_full[2], stage_free[2], s_ready, dp_ready, pds_ready, mma2_done, dq_done;
   uint32_t tmem_base;
   int err;
   int qt_first, n_qt;
 };
 
-// K, V, 2 x (Q, dO), dS  +  2 x (lse, delta) rows  +  control
+// K, V, 2 x (Q, dO), dS  +  2 stages x (lse2, delta) rows  +  control
 constexpr int kBwdSmemTiles = 7 * kTileBytes;
-constexpr int kBwdSmemBytes = kBwdSmemTiles + 2 * 2 * kTile * 4 + 256;
+constexpr int kRowBytes = kTile * 4;
+constexpr int kBwdSmemBytes = kBwdSmemTiles + 2 * 2 * kRowBytes + 256;
+constexpr uint32_t kStageTxBytes = 2 * kTileBytes + 2 * kRowBytes;
 static_assert(sizeof(BwdCtl) <= 256, "control block too large");
 static_assert(kBwdSmemBytes <= 232448, "shared memory budget");
 
@@ -61,7 +72,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   uint8_t* sDS = smem + 6 * kTileBytes;
   float* sLse = reinterpret_cast<float*>(smem + kBwdSmemTiles);  // [2][128]
   float* sDelta = sLse + 2 * kTile;                              // [2][128]
-  BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + kBwdSmemTiles + 2 * 2 * kTile * 4);
+  BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + kBwdSmemTiles + 2 * 2 * kRowBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -87,10 +98,11 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     mbar_init(&ctl->qdo_full[1], 1);
     mbar_init(&ctl->stage_free[0], 1);
     mbar_init(&ctl->stage_free[1], 1);
-    mbar_init(&ctl->sdp_ready, 1);
-    mbar_init(&ctl->pds_ready, 256);
+    mbar_init(&ctl->s_ready, 1);
+    mbar_init(&ctl->dp_ready, 1);
+    mbar_init(&ctl->pds_ready, kComputeThreads);
     mbar_init(&ctl->mma2_done, 1);
-    mbar_init(&ctl->dq_done, 256);
+    mbar_init(&ctl->dq_done, kReduceThreads);
     ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
     mbar_fence_init();
     // query tiles that can see at least one key of this tile
@@ -129,93 +141,99 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   const int n_qt = (ctl->err != 0) ? 0 : ctl->n_qt;
   const int n_iter = n_qt * group;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_iter > 0) {
-      mbar_expect_tx(&ctl->kv_full, 2 * kTileBytes);
-      tma_load_4d(sK, &p.k_map[sp], &ctl->kv_full, 0, hk, key0, b);
-      tma_load_4d(sK + kBoxBytes, &p.k_map[sp], &ctl->kv_full, 64, hk, key0, b);
-      tma_load_4d(sV, &p.v_map[sp], &ctl->kv_full, 0, hk, key0, b);
-      tma_load_4d(sV + kBoxBytes, &p.v_map[sp], &ctl->kv_full, 64, hk, key0, b);
-      bool ok = true;
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int st = it & 1;
-        const int h = hk * group + it / n_qt;
-        const int row0 = (qt_first + it % n_qt) * kTile;
-        if (it >= 2) ok = mbar_wait(&ctl->stage_free[st], ((it >> 1) - 1) & 1, err, kErrWaitProducer);
-        if (!ok) break;
-        mbar_expect_tx(&ctl->qdo_full[st], 2 * kTileBytes);
-        uint8_t* q_dst = sQ + st * kTileBytes;
-        uint8_t* do_dst = sDO + st * kTileBytes;
-        tma_load_4d(q_dst, &p.q_map, &ctl->qdo_full[st], 0, h, row0, b);
-        tma_load_4d(q_dst + kBoxBytes, &p.q_map, &ctl->qdo_full[st], 64, h, row0, b);
-        tma_load_4d(do_dst, &p.do_map, &ctl->qdo_full[st], 0, h, row0, b);
-        tma_load_4d(do_dst + kBoxBytes, &p.do_map, &ctl->qdo_full[st], 64, h, row0, b);
+  if (warp < 4) {
+    setmaxnreg_dec<48>();
+    if (warp == 0) {
+      // ---------------------------------------------------------------- TMA producer
+      if (lane == 0 && n_iter > 0) {
+        mbar_expect_tx(&ctl->kv_full, 2 * kTileBytes);
+        tma_load_4d(sK, &p.k_map[sp], &ctl->kv_full, 0, hk, key0, b);
+        tma_load_4d(sK + kBoxBytes, &p.k_map[sp], &ctl->kv_full, 64, hk, key0, b);
+        tma_load_4d(sV, &p.v_map[sp], &ctl->kv_full, 0, hk, key0, b);
+        tma_load_4d(sV + kBoxBytes, &p.v_map[sp], &ctl->kv_full, 64, hk, key0, b);
+        bool ok = true;
+        for (int it = 0; it < n_iter && ok; ++it) {
+          const int st = it & 1;
+          const int h = hk * group + it / n_qt;
+          const int row0 = (qt_first + it % n_qt) * kTile;
+          if (it >= 2) ok = mbar_wait(&ctl->stage_free[st], ((it >> 1) - 1) & 1, err, kErrWaitProducer);
+          if (!ok) break;
+          mbar_expect_tx(&ctl->qdo_full[st], kStageTxBytes);
+          uint8_t* q_dst = sQ + st * kTileBytes;
+          uint8_t* do_dst = sDO + st * kTileBytes;
+          tma_load_4d(q_dst, &p.q_map, &ctl->qdo_full[st], 0, h, row0, b);
+          tma_load_4d(q_dst + kBoxBytes, &p.q_map, &ctl->qdo_full[st], 64, h, row0, b);
+          tma_load_4d(do_dst, &p.do_map, &ctl->qdo_full[st], 0, h, row0, b);
+          tma_load_4d(do_dst + kBoxBytes, &p.do_map, &ctl->qdo_full[st], 64, h, row0, b);
+          const long long roff = b * p.d_sb + h * p.d_sh + row0;
+          bulk_load_1d(sLse + st * kTile, p.lse2 + roff, kRowBytes, &ctl->qdo_full[st]);
+          bulk_load_1d(sDelta + st * kTile, p.delta + roff, kRowBytes, &ctl->qdo_full[st]);
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------------------------------------------------------- MMA issuer
+      if (lane == 0 && n_iter > 0) {
+        constexpr int bf = kBf16 ? 1 : 0;
+        constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);  // both operands K-major
+        constexpr uint32_t id_tn = idesc_f16(128, 128, bf, 0, 1);  // A from TMEM, B MN-major
+        constexpr uint32_t id_nn = idesc_f16(128, 128, bf, 1, 1);  // both MN-major
+        const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
+        bool ok = mbar_wait(&ctl->kv_full, 0, err, kErrWaitMma);
+        for (int it = 0; it < n_iter && ok; ++it) {
+          const int st = it & 1;
+          const uint32_t aQ = smem_u32(sQ + st * kTileBytes), aDO = smem_u32(sDO + st * kTileBytes);
+          ok = mbar_wait(&ctl->qdo_full[st], (it >> 1) & 1, err, kErrWaitMma);
+          if (!ok) break;
+          tc_fence_after();
+          // S^T: overwrites the columns P^T / dS^T of the previous tile lived in; the MMAs reading
+          // them were issued earlier by this thread and therefore execute first
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
+            mma_ss(tA, smem_desc_sw128(aK + off, 16, 1024), smem_desc_sw128(aQ + off, 16, 1024), id_kk,
+                   k > 0 ? 1u : 0u);
+          }
+          mma_commit(&ctl->s_ready);
+          // dQ of the previous tile lives where dP^T goes: wait until it has been read out
+          if (it > 0) ok = mbar_wait(&ctl->dq_done, (it - 1) & 1, err, kErrWaitMma);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
+            mma_ss(tB, smem_desc_sw128(aV + off, 16, 1024), smem_desc_sw128(aDO + off, 16, 1024), id_kk,
+                   k > 0 ? 1u : 0u);
+          }
+          mma_commit(&ctl->dp_ready);
+          ok = mbar_wait(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // dV += P^T dO
+            mma_ts(tDV, tP + k * 8, smem_desc_sw128(aDO + k * 2048, kBoxBytes, 1024), id_tn,
+                   (it > 0 || k > 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // dK += dS^T Q
+            mma_ts(tDK, tDS + k * 8, smem_desc_sw128(aQ + k * 2048, kBoxBytes, 1024), id_tn,
+                   (it > 0 || k > 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {  // dQ = dS K
+            mma_ss(tB, smem_desc_sw128(aDS + k * 2048, kBoxBytes, 1024),
+                   smem_desc_sw128(aK + k * 2048, kBoxBytes, 1024), id_nn, k > 0 ? 1u : 0u);
+          }
+          mma_commit(&ctl->mma2_done);
+          mma_commit(&ctl->stage_free[st]);
+        }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_iter > 0) {
-      constexpr int bf = kBf16 ? 1 : 0;
-      constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);  // both operands K-major
-      constexpr uint32_t id_tn = idesc_f16(128, 128, bf, 0, 1);  // A from TMEM, B MN-major
-      constexpr uint32_t id_nn = idesc_f16(128, 128, bf, 1, 1);  // both MN-major
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
-      bool ok = mbar_wait(&ctl->kv_full, 0, err, kErrWaitMma);
-      for (int it = 0; it < n_iter && ok; ++it) {
-        const int st = it & 1;
-        const uint32_t aQ = smem_u32(sQ + st * kTileBytes), aDO = smem_u32(sDO + st * kTileBytes);
-        ok = mbar_wait(&ctl->qdo_full[st], (it >> 1) & 1, err, kErrWaitMma);
-        if (!ok) break;
-        // P^T / dS^T of the previous iteration live where S^T goes: wait for the MMAs reading them
-        if (it > 0) ok = mbar_wait(&ctl->mma2_done, (it - 1) & 1, err, kErrWaitMma);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-          mma_ss(tA, smem_desc_sw128(aK + off, 16, 1024), smem_desc_sw128(aQ + off, 16, 1024), id_kk,
-                 k > 0 ? 1u : 0u);
-        }
-        // dQ of the previous iteration lives where dP^T goes: wait until it has been read out
-        if (it > 0) ok = mbar_wait(&ctl->dq_done, (it - 1) & 1, err, kErrWaitMma);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-          mma_ss(tB, smem_desc_sw128(aV + off, 16, 1024), smem_desc_sw128(aDO + off, 16, 1024), id_kk,
-                 k > 0 ? 1u : 0u);
-        }
-        mma_commit(&ctl->sdp_ready);
-        ok = mbar_wait(&ctl->pds_ready, it & 1, err, kErrWaitMma);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dV += P^T dO
-          mma_ts(tDV, tP + k * 8, smem_desc_sw128(aDO + k * 2048, kBoxBytes, 1024), id_tn,
-                 (it > 0 || k > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dK += dS^T Q
-          mma_ts(tDK, tDS + k * 8, smem_desc_sw128(aQ + k * 2048, kBoxBytes, 1024), id_tn,
-                 (it > 0 || k > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dQ = dS K
-          mma_ss(tB, smem_desc_sw128(aDS + k * 2048, kBoxBytes, 1024),
-                 smem_desc_sw128(aK + k * 2048, kBoxBytes, 1024), id_nn, k > 0 ? 1u : 0u);
-        }
-        mma_commit(&ctl->mma2_done);
-        mma_commit(&ctl->stage_free[st]);
-      }
-    }
-  } else {
+  } else if (warp < 12) {
     // ------------------------------------------------------------------ compute warps
+    setmaxnreg_inc<200>();
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;            // which 64 columns of the 128 this warp handles
-    const int row = quad * 32 + lane;            // key row (S^T, dK, dV) or query row (dQ)
-    const int ctid = threadIdx.x - 64;           // 0..255
+    const int half = (warp - 4) >> 2;            // which 64 query columns this warp handles
+    const int row = quad * 32 + lane;            // key row
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const bool valid_k = row < n_valid_k;
     const int t = valid_k ? t0 + row : 0x7fffffff;
@@ -232,60 +250,76 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     bool ok = true;
 
     for (int it = 0; it < n_iter && ok; ++it) {
-      const int h = hk * group + it / n_qt;
       const int qrow0 = (qt_first + it % n_qt) * kTile;
       const int pq0 = p.q_pos_start + qrow0;
-      float* lse_s = sLse + (it & 1) * kTile;
-      float* del_s = sDelta + (it & 1) * kTile;
-      {
-        const int qi = ctid & 127;
-        const bool qv = qrow0 + qi < p.q_len;
-        if (ctid < 128) {
-          lse_s[qi] = qv ? p.lse[b * p.l_sb + h * p.l_sh + qrow0 + qi] * 1.4426950408889634f : INFINITY;
-        } else {
-          del_s[qi] = qv ? p.delta[b * p.d_sb + h * p.d_sh + qrow0 + qi] : 0.f;
-        }
-      }
-      ok = mbar_wait(&ctl->sdp_ready, it & 1, err, kErrWaitSoftmax);
+      const float* lse_s = sLse + (it & 1) * kTile + half * 64;
+      const float* del_s = sDelta + (it & 1) * kTile + half * 64;
+      const bool full = (pq0 >= t) && (pq0 + kTile - 1 <= p_hi);
+      const bool masked = !__all_sync(0xffffffffu, full);
+
+      // P^T from S^T (the lse2 / delta rows of this stage landed before S^T was issued)
+      ok = mbar_wait(&ctl->s_ready, it & 1, err, kErrWaitSoftmax);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t s[64], dp[64];
+      float pr[64];
       {
-        uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
-        uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
-        uint32_t(&d0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&dp[0]);
-        uint32_t(&d1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&dp[32]);
+        uint32_t s0[32], s1[32];
         tmem_ld32(tA + lane_off + half * 64, s0);
         tmem_ld32(tA + lane_off + half * 64 + 32, s1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 la = *reinterpret_cast<const float4*>(lse_s + i);
+          const float4 lb = *reinterpret_cast<const float4*>(lse_s + i + 32);
+          pr[i + 0] = ex2f(fmaf(__uint_as_float(s0[i + 0]), sl2, -la.x));
+          pr[i + 1] = ex2f(fmaf(__uint_as_float(s0[i + 1]), sl2, -la.y));
+          pr[i + 2] = ex2f(fmaf(__uint_as_float(s0[i + 2]), sl2, -la.z));
+          pr[i + 3] = ex2f(fmaf(__uint_as_float(s0[i + 3]), sl2, -la.w));
+          pr[i + 32] = ex2f(fmaf(__uint_as_float(s1[i + 0]), sl2, -lb.x));
+          pr[i + 33] = ex2f(fmaf(__uint_as_float(s1[i + 1]), sl2, -lb.y));
+          pr[i + 34] = ex2f(fmaf(__uint_as_float(s1[i + 2]), sl2, -lb.z));
+          pr[i + 35] = ex2f(fmaf(__uint_as_float(s1[i + 3]), sl2, -lb.w));
+        }
+      }
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int pq = pq0 + half * 64 + i;
+          pr[i] = (pq >= t && pq <= p_hi) ? pr[i] : 0.f;
+        }
+      }
+      // dS^T = P^T * (dP^T - delta)
+      ok = mbar_wait(&ctl->dp_ready, it & 1, err, kErrWaitSoftmax);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t dpk[32];
+      {
+        uint32_t d0[32], d1[32];
         tmem_ld32(tB + lane_off + half * 64, d0);
         tmem_ld32(tB + lane_off + half * 64 + 32, d1);
         tmem_ld_wait();
-      }
-      tc_fence_before();
-      bar_sync_compute();  // lse/delta rows are in smem; every warp has read S^T and dP^T
-      tc_fence_after();
-
-      const bool full = (pq0 >= t) && (pq0 + kTile - 1 <= p_hi);
-      const bool masked = !__all_sync(0xffffffffu, full);
-      uint32_t ppk[32], dpk[32];
 #pragma unroll
-      for (int i = 0; i < 64; i += 2) {
-        const int q = half * 64 + i;
-        const float2 l2 = *reinterpret_cast<const float2*>(lse_s + q);
-        const float2 dl = *reinterpret_cast<const float2*>(del_s + q);
-        float p0 = ex2f(fmaf(__uint_as_float(s[i]), sl2, -l2.x));
-        float p1 = ex2f(fmaf(__uint_as_float(s[i + 1]), sl2, -l2.y));
-        if (masked) {
-          const int pq = pq0 + q;
-          p0 = (pq >= t && pq <= p_hi) ? p0 : 0.f;
-          p1 = (pq + 1 >= t && pq + 1 <= p_hi) ? p1 : 0.f;
+        for (int i = 0; i < 32; i += 4) {
+          const float4 da = *reinterpret_cast<const float4*>(del_s + i);
+          const float4 db = *reinterpret_cast<const float4*>(del_s + i + 32);
+          dpk[(i >> 1) + 0] = pack2<kBf16>(pr[i + 0] * (__uint_as_float(d0[i + 0]) - da.x),
+                                           pr[i + 1] * (__uint_as_float(d0[i + 1]) - da.y));
+          dpk[(i >> 1) + 1] = pack2<kBf16>(pr[i + 2] * (__uint_as_float(d0[i + 2]) - da.z),
+                                           pr[i + 3] * (__uint_as_float(d0[i + 3]) - da.w));
+          dpk[(i >> 1) + 16] = pack2<kBf16>(pr[i + 32] * (__uint_as_float(d1[i + 0]) - db.x),
+                                            pr[i + 33] * (__uint_as_float(d1[i + 1]) - db.y));
+          dpk[(i >> 1) + 17] = pack2<kBf16>(pr[i + 34] * (__uint_as_float(d1[i + 2]) - db.z),
+                                            pr[i + 35] * (__uint_as_float(d1[i + 3]) - db.w));
         }
-        const float ds0 = p0 * (__uint_as_float(dp[i]) - dl.x);
-        const float ds1 = p1 * (__uint_as_float(dp[i + 1]) - dl.y);
-        ppk[i >> 1] = pack2<kBf16>(p0, p1);
-        dpk[i >> 1] = pack2<kBf16>(ds0, ds1);
       }
+      uint32_t ppk[32];
+#pragma unroll
+      for (int i = 0; i < 64; i += 2) ppk[i >> 1] = pack2<kBf16>(pr[i], pr[i + 1]);
+      tc_fence_before();
+      bar_sync_compute();  // every compute warp has read its part of S^T and dP^T
+      tc_fence_after();
       tmem_st32(tP + lane_off + half * 32, ppk);
       tmem_st32(tDS + lane_off + half * 32, dpk);
       // dS^T also goes to shared memory ([key][query], query contiguous, 128-byte swizzle) as the
@@ -299,36 +333,12 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&ctl->pds_ready);
-
-      // dQ tile -> fp32 accumulator in global memory
-      ok = mbar_wait(&ctl->mma2_done, it & 1, err, kErrWaitEpilogue);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      {
-        const bool qv = qrow0 + row < p.q_len;
-        float* dst = p.dq_acc + ((static_cast<long long>(b) * p.q_len + qrow0 + row) * p.hq + h) * kHeadDim +
-                     half * 64;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tB + lane_off + half * 64 + c * 32, r);
-          tmem_ld_wait();
-          if (qv) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v) {
-              red_add_v4(dst + c * 32 + v * 4, __uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
-                         __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(&ctl->dq_done);
     }
 
     // epilogue: dK (scaled) and dV for this key tile
+    if (ok && n_iter > 0) ok = mbar_wait(&ctl->mma2_done, (n_iter - 1) & 1, err, kErrWaitEpilogue);
     ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
     if (ok && ctl->err == 0) {
       const long long off = b * p.dkv_sb[sp] + static_cast<long long>(key0 + row) * p.dkv_st[sp] +
                             hk * p.dkv_sh[sp] + half * 64;
@@ -367,6 +377,40 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
                 dst[v] = o;
               }
             }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ dQ reduction warps
+    setmaxnreg_dec<64>();
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;  // query row inside the tile
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int h = hk * group + it / n_qt;
+      const int qrow0 = (qt_first + it % n_qt) * kTile;
+      const bool qv = qrow0 + row < p.q_len;
+      float* dst = p.dq_acc + ((static_cast<long long>(b) * p.q_len + qrow0 + row) * p.hq + h) * kHeadDim;
+      ok = mbar_wait(&ctl->mma2_done, it & 1, err, kErrWaitEpilogue);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tB + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (c == 3) {  // the whole tile is in registers: the MMA thread may overwrite it
+          tc_fence_before();
+          mbar_arrive(&ctl->dq_done);
+        }
+        if (qv) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            red_add_v4(dst + c * 32 + v * 4, __uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
+                       __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
           }
         }
       }

@@ -61,9 +61,10 @@ struct BwdKernelParams {
   float scale;
   const int* cu;
   int n_seqs;
-  const float* lse;
-  long long l_sb, l_sh;
-  const float* delta;  // [batch, hq, q_len_pad]
+  // rows prepared by the delta kernel, both [batch, hq, q_len_pad] fp32, 512-byte aligned per
+  // 128-query tile: lse * log2(e) (+inf past q_len) and delta = rowsum(dO * O) (0 past q_len)
+  const float* lse2;
+  const float* delta;
   long long d_sb, d_sh;
   float* dq_acc;  // [batch, q_len, hq, 128] contiguous fp32
   int* status;
