@@ -74,6 +74,9 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   float* sDelta = sLse + 2 * kTile;                              // [2][128]
   BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + kBwdSmemTiles + 2 * 2 * kRowBytes);
 
+  // a device-side error was already reported on this stream: do not pile further time-outs on it
+  if (__syncthreads_or(*reinterpret_cast<volatile int*>(p.status) != 0)) return;
+
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 

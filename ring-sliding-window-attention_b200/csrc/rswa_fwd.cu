@@ -1,20 +1,27 @@
-// Forward kernel: banded (sliding-window + sink) softmax attention for one 128-row query tile per
-// CTA on the sm_100a tensor cores.
+// Forward kernel: banded (sliding-window + sink) softmax attention on the sm_100a tensor cores.
 //
-//   S = Q K^T      tcgen05.mma, both operands in shared memory (K-major), accumulator in TMEM
-//   P = softmax    four warps, one query row per thread, read S from TMEM, write P (16-bit) back
-//                  into the same TMEM columns
-//   O += P V       tcgen05.mma, A = P from TMEM, B = V from shared memory (MN-major)
+// One CTA owns two consecutive 128-row query tiles of one head and walks the key tiles either of
+// them can see.  Two softmax warp groups (one per query tile) work in ping-pong against a single
+// MMA-issuing thread, so that the tensor cores compute one tile's products while the other tile's
+// exponentials run:
 //
-// Key tiles that no row of the query tile can see are never loaded: the visible keys of a query
-// tile are one contiguous run of global positions (plus the sink tokens), intersected with each
-// KV span.  Two CTAs share an SM (96 KB of shared memory and 256 TMEM columns each) so that one
-// CTA's softmax overlaps the other's MMAs.
+//   S_w = Q_w K^T      tcgen05.mma, both operands in shared memory (K-major), accumulator in TMEM
+//   P_w = softmax      warp group w: one query row per thread, whole S row in registers, P written
+//                      back (16-bit) over the same TMEM columns
+//   O_w += P_w V       tcgen05.mma, A = P_w from TMEM, B = V from shared memory (MN-major)
 //
-// The math follows the reference's dense oracle (test/test_local_swa.py:51-93): scores scaled by
-// softmax_scale, keys outside [p - W, p] masked to -inf (the sink column forced on,
-// test/test_local_slm.py:62-64), fp32 softmax, P rounded to the value dtype before P V.
+// The MMA thread issues S_w of the NEXT key tile right behind O_w += P_w V of the current one
+// (tcgen05.mma instructions of one thread execute in issue order, so the overwrite of P_w's columns
+// cannot overtake its last reader).  K and V tiles travel through two-stage TMA rings.
+// TMEM: [0,128) S_0/P_0, [128,256) S_1/P_1, [256,384) O_0, [384,512) O_1.
+//
+// Key tiles that no row of the block can see are never loaded (rswa_tiles.cuh); a query tile skips
+// the key tiles only the other one needs.  The math follows the reference's dense oracle
+// (test/test_local_swa.py:51-93): scores scaled by softmax_scale, keys outside [p - W, p] masked
+// (the sink columns forced on, test/test_local_slm.py:62-64), fp32 softmax, P rounded to the
+// value dtype before P V.
 #include "rswa_common.cuh"
+#include "rswa_tiles.cuh"
 #include "tc05.cuh"
 
 namespace rswa {
@@ -22,98 +29,67 @@ using namespace tc05;
 
 namespace {
 
-constexpr int kFwdThreads = 192;  // warp 0: TMA, warp 1: MMA, warps 2-5: softmax
-constexpr int kFwdTmemCols = 256; // [0,128) S / P, [128,256) O
+constexpr int kFwdThreads = 384;   // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-7 / 8-11 softmax
+constexpr int kFwdTmemCols = 512;
+constexpr int kFwdSmemTiles = 6 * kTileBytes;  // Q_0, Q_1, K x 2, V x 2
 
 struct FwdCtl {
-  uint64_t q_full, k_full, v_full, s_ready, pv_done, p_ready;
+  uint64_t q_full, k_full[2], v_full[2], k_free[2], v_free[2], s_ready[2], p_ready[2], pv_done[2];
   uint32_t tmem_base;
   int err;
-  int n_entries;
-  int n_tiles;
-  int ent_span[kMaxEntries];
-  int ent_first[kMaxEntries];
-  int ent_count[kMaxEntries];
+  QBlockGeom geom;
 };
 
-constexpr int kFwdSmemBytes = 3 * kTileBytes + 1024 /*alignment slack*/ + 1024 /*FwdCtl*/;
+constexpr int kFwdSmemBytes = kFwdSmemTiles + 1024;
 static_assert(sizeof(FwdCtl) <= 1024, "control block too large");
+static_assert(kFwdSmemBytes <= 232448, "shared memory budget");
+
+// visible(p, t) for the row owning (lo, hi, seq, sink_end): t in [lo, hi] or a sink position <= hi
+__device__ __forceinline__ bool key_visible(int t, int lo, int hi, int seq, int sink_end, int span_end) {
+  return t <= hi && t < span_end && (t >= lo || (t >= seq && t < sink_end));
+}
 
 template <bool kBf16>
-__global__ void __launch_bounds__(kFwdThreads, 2)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + kTileBytes;
-  uint8_t* sV = smem + 2 * kTileBytes;
-  FwdCtl* ctl = reinterpret_cast<FwdCtl*>(smem + 3 * kTileBytes);
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem;                     // two query tiles
+  uint8_t* sK = smem + 2 * kTileBytes;    // two stages
+  uint8_t* sV = smem + 4 * kTileBytes;    // two stages
+  FwdCtl* ctl = reinterpret_cast<FwdCtl*>(smem + kFwdSmemTiles);
+  QBlockGeom* geom = &ctl->geom;
+
+  // a device-side error was already reported on this stream: do not pile further time-outs on it
+  if (__syncthreads_or(*reinterpret_cast<volatile int*>(p.status) != 0)) return;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // work item: query tile fastest, then head, then batch row
+  // work item: query block fastest, then head, then batch row
+  const int n_blocks = (p.n_q_tiles + 1) >> 1;
   int idx = blockIdx.x;
-  const int qt = p.q_tile_begin + idx % p.n_q_tiles;
-  idx /= p.n_q_tiles;
+  const int blk = idx % n_blocks;
+  idx /= n_blocks;
   const int h = idx % p.hq;
   const int b = idx / p.hq;
   const int hk = h / (p.hq / p.hkv);
-
-  const int row0 = qt * kTile;
-  const int n_valid = min(kTile, p.q_len - row0);
-  const int p0 = p.q_pos_start + row0;
-  const int p_last = p0 + n_valid - 1;
+  const int tile0 = p.q_tile_begin + 2 * blk;
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
-    mbar_init(&ctl->k_full, 1);
-    mbar_init(&ctl->v_full, 1);
-    mbar_init(&ctl->s_ready, 1);
-    mbar_init(&ctl->pv_done, 1);
-    mbar_init(&ctl->p_ready, 128);
-    ctl->err = 0;
-    mbar_fence_init();
-    // Key tiles this query tile needs, per span: the sink tiles that lie below the window
-    // tiles, then the window tiles.  Tiles are 128-aligned relative to the span start.
-    int s0, e0;
-    seq_of(p.cu, p.n_seqs, p0, s0, e0);
-    const int min_lo = max(s0, p0 - p.window);
-    int ne = 0, nt = 0;
-    for (int i = 0; i < p.n_spans; ++i) {
-      const int a = p.span_pos[i], bnd = a + p.span_len[i];
-      int wfirst = -1, wlast = -1;
-      const int wl = max(min_lo, a), wh = min(p_last, bnd - 1);
-      if (wl <= wh) {
-        wfirst = (wl - a) / kTile;
-        wlast = (wh - a) / kTile;
-      }
-      if (p.n_sink > 0) {
-        const int sl = max(s0, a), sh = min(min(s0 + p.n_sink - 1, bnd - 1), p_last);
-        if (sl <= sh) {
-          const int sf = (sl - a) / kTile;
-          int slast = (sh - a) / kTile;
-          if (wfirst >= 0) slast = min(slast, wfirst - 1);
-          if (sf <= slast) {
-            ctl->ent_span[ne] = i;
-            ctl->ent_first[ne] = sf;
-            ctl->ent_count[ne] = slast - sf + 1;
-            nt += slast - sf + 1;
-            ++ne;
-          }
-        }
-      }
-      if (wfirst >= 0) {
-        ctl->ent_span[ne] = i;
-        ctl->ent_first[ne] = wfirst;
-        ctl->ent_count[ne] = wlast - wfirst + 1;
-        nt += wlast - wfirst + 1;
-        ++ne;
-      }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctl->k_full[i], 1);
+      mbar_init(&ctl->v_full[i], 1);
+      mbar_init(&ctl->k_free[i], 1);
+      mbar_init(&ctl->v_free[i], 1);
+      mbar_init(&ctl->s_ready[i], 1);
+      mbar_init(&ctl->p_ready[i], 128);
+      mbar_init(&ctl->pv_done[i], 1);
     }
-    ctl->n_entries = ne;
-    ctl->n_tiles = nt;
+    ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
+    mbar_fence_init();
+    qblock_geometry<kTile>(geom, p.cu, p.n_seqs, p.n_spans, p.span_pos, p.span_len, p.q_pos_start, p.q_len,
+                           p.window, p.n_sink, tile0, p.q_tile_begin + p.n_q_tiles);
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, kFwdTmemCols);
@@ -124,215 +100,240 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   tc_fence_after();
 
   const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tS = tmem;
-  const uint32_t tO = tmem + 128;
   volatile int* err = &ctl->err;
-  const int n_entries = ctl->n_entries;
-  const int n_tiles = ctl->n_tiles;
+  const int n_tiles = (ctl->err != 0) ? 0 : geom->n_tiles;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_tiles > 0) {
-      prefetch_tmap(&p.q_map);
-      mbar_expect_tx(&ctl->q_full, kTileBytes);
-      tma_load_4d(sQ, &p.q_map, &ctl->q_full, 0, h, row0, b);
-      tma_load_4d(sQ + kBoxBytes, &p.q_map, &ctl->q_full, 64, h, row0, b);
-      int j = 0;
-      bool ok = true;
-      for (int e = 0; e < n_entries && ok; ++e) {
-        const int sp = ctl->ent_span[e];
-        for (int t = 0; t < ctl->ent_count[e] && ok; ++t, ++j) {
-          const int tok = (ctl->ent_first[e] + t) * kTile;
-          // K buffer is free once S(j-1) has been produced from it
-          if (j > 0) ok = mbar_wait(&ctl->s_ready, (j - 1) & 1, err, kErrWaitProducer);
-          if (!ok) break;
-          mbar_expect_tx(&ctl->k_full, kTileBytes);
-          tma_load_4d(sK, &p.k_map[sp], &ctl->k_full, 0, hk, tok, b);
-          tma_load_4d(sK + kBoxBytes, &p.k_map[sp], &ctl->k_full, 64, hk, tok, b);
-          // V buffer is free once O += P(j-1) V(j-1) has completed
-          if (j > 0) ok = mbar_wait(&ctl->pv_done, (j - 1) & 1, err, kErrWaitProducer);
-          if (!ok) break;
-          mbar_expect_tx(&ctl->v_full, kTileBytes);
-          tma_load_4d(sV, &p.v_map[sp], &ctl->v_full, 0, hk, tok, b);
-          tma_load_4d(sV + kBoxBytes, &p.v_map[sp], &ctl->v_full, 64, hk, tok, b);
-        }
+  if (warp < 4) {
+    setmaxnreg_dec<48>();
+    if (warp == 0 && lane == 0 && n_tiles > 0) {
+      // ------------------------------------------------------------------ TMA producer
+      const bool two = geom->n_valid[1] > 0;
+      mbar_expect_tx(&ctl->q_full, two ? 2 * kTileBytes : kTileBytes);
+      tma_load_4d(sQ, &p.q_map, &ctl->q_full, 0, h, tile0 * kTile, b);
+      tma_load_4d(sQ + kBoxBytes, &p.q_map, &ctl->q_full, 64, h, tile0 * kTile, b);
+      if (two) {
+        tma_load_4d(sQ + kTileBytes, &p.q_map, &ctl->q_full, 0, h, (tile0 + 1) * kTile, b);
+        tma_load_4d(sQ + kTileBytes + kBoxBytes, &p.q_map, &ctl->q_full, 64, h, (tile0 + 1) * kTile, b);
       }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_tiles > 0) {
+      TileCursor c;
+      cursor_begin<kTile>(geom, p.span_pos, p.span_len, c);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        if (j >= 2) ok = mbar_wait(&ctl->k_free[st], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
+        if (!ok) break;
+        mbar_expect_tx(&ctl->k_full[st], kTileBytes);
+        tma_load_4d(sK + st * kTileBytes, &p.k_map[c.span], &ctl->k_full[st], 0, hk, c.tok, b);
+        tma_load_4d(sK + st * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[st], 64, hk, c.tok, b);
+        if (j >= 2) ok = mbar_wait(&ctl->v_free[st], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
+        if (!ok) break;
+        mbar_expect_tx(&ctl->v_full[st], kTileBytes);
+        tma_load_4d(sV + st * kTileBytes, &p.v_map[c.span], &ctl->v_full[st], 0, hk, c.tok, b);
+        tma_load_4d(sV + st * kTileBytes + kBoxBytes, &p.v_map[c.span], &ctl->v_full[st], 64, hk, c.tok, b);
+        cursor_next<kTile>(geom, p.span_pos, p.span_len, c, j + 1 < n_tiles);
+      }
+    } else if (warp == 1 && lane == 0 && n_tiles > 0) {
+      // ------------------------------------------------------------------ MMA issuer
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t idesc_pv = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+      int n_pv[2] = {0, 0};  // products O_w += P_w V issued so far (also the phase of p_ready[w])
+      TileCursor cur, nxt;
+      cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
       bool ok = mbar_wait(&ctl->q_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait(&ctl->k_full[0], 0, err, kErrWaitMma);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int w = 0; w < 2; ++w) {
+          if (tile_active(geom, w, cur, p.n_sink)) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
+              mma_ss(tmem + 128 * w, smem_desc_sw128(aQ + w * kTileBytes + off, 16, 1024),
+                     smem_desc_sw128(aK + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+            }
+            mma_commit(&ctl->s_ready[w]);
+          }
+        }
+        mma_commit(&ctl->k_free[0]);
+      }
       for (int j = 0; j < n_tiles && ok; ++j) {
-        // P(j-1) shares TMEM columns with S(j): wait until the previous P V has drained
-        if (j > 0) ok = mbar_wait(&ctl->pv_done, (j - 1) & 1, err, kErrWaitMma);
+        const bool more = j + 1 < n_tiles;
+        const int sv = j & 1, sk = (j + 1) & 1;
+        nxt = cur;
+        cursor_next<kTile>(geom, p.span_pos, p.span_len, nxt, more);
+        ok = mbar_wait(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
+        if (ok && more) ok = mbar_wait(&ctl->k_full[sk], ((j + 1) >> 1) & 1, err, kErrWaitMma);
         if (!ok) break;
-        ok = mbar_wait(&ctl->k_full, j & 1, err, kErrWaitMma);
-        if (!ok) break;
-        tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-          mma_ss(tS, smem_desc_sw128(aQ + off, 16, 1024), smem_desc_sw128(aK + off, 16, 1024),
-                 idesc_qk, k > 0 ? 1u : 0u);
-        }
-        mma_commit(&ctl->s_ready);
-        ok = mbar_wait(&ctl->v_full, j & 1, err, kErrWaitMma);
-        if (!ok) break;
-        ok = mbar_wait(&ctl->p_ready, j & 1, err, kErrWaitMma);
-        if (!ok) break;
-        tc_fence_after();
+        for (int w = 0; w < 2; ++w) {
+          if (tile_active(geom, w, cur, p.n_sink)) {
+            ok = mbar_wait(&ctl->p_ready[w], n_pv[w] & 1, err, kErrWaitMma);
+            if (!ok) break;
+            tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          mma_ts(tO, tS + k * 8, smem_desc_sw128(aV + k * 2048, kBoxBytes, 1024), idesc_pv,
-                 (j > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 8; ++k) {
+              mma_ts(tmem + 256 + 128 * w, tmem + 128 * w + k * 8,
+                     smem_desc_sw128(aV + sv * kTileBytes + k * 2048, kBoxBytes, 1024), idesc_pv,
+                     (n_pv[w] > 0 || k > 0) ? 1u : 0u);
+            }
+            mma_commit(&ctl->pv_done[w]);
+            ++n_pv[w];
+          }
+          if (more && tile_active(geom, w, nxt, p.n_sink)) {
+            // overwrites P_w of the current tile: ordered behind the product just issued
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
+              mma_ss(tmem + 128 * w, smem_desc_sw128(aQ + w * kTileBytes + off, 16, 1024),
+                     smem_desc_sw128(aK + sk * kTileBytes + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+            }
+            mma_commit(&ctl->s_ready[w]);
+          }
         }
-        mma_commit(&ctl->pv_done);
+        if (!ok) break;
+        mma_commit(&ctl->v_free[sv]);
+        if (more) mma_commit(&ctl->k_free[sk]);
+        cur = nxt;
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue
+    // -------------------------------------------------------------------- softmax warp groups
+    setmaxnreg_inc<224>();  // 128 x 48 + 256 x 224 <= 384 x 168 (the launch allocation)
+    const int w = (warp - 4) >> 2;          // query tile of the block this warp group owns
     const int quad = warp & 3;              // TMEM lane quadrant this warp may touch
     const int row = quad * 32 + lane;       // query row inside the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    const bool valid = row < n_valid;
-    const int pos = p0 + row;
+    const uint32_t tS = tmem + 128 * w + lane_off;
+    const uint32_t tO = tmem + 256 + 128 * w + lane_off;
+    const bool valid = row < geom->n_valid[w];
+    const int pos = geom->p0[w] + row;
     int s_p = 0, e_p = 0;
     if (valid) seq_of(p.cu, p.n_seqs, pos, s_p, e_p);
-    // visible keys: [lo, hi] plus [s_p, sink_end) (both clipped by t <= pos)
+    // visible keys: [lo, hi] plus the sink positions [s_p, sink_end), all <= pos
     const int hi = valid ? pos : -1;
     const int lo = valid ? max(s_p, pos - p.window) : 0x7fffffff;
     const int sink_end = valid ? s_p + p.n_sink : -0x7fffffff;
     const float sl2 = p.scale_log2;
 
-    float m_ref = -INFINITY;  // reference maximum, in log2 units (already scaled)
+    float m_ref = -INFINITY;  // reference maximum in log2 units (already scaled)
     float l_sum = 0.f;
+    int n_done = 0;           // key tiles this warp group has processed
     bool ok = true;
-    int j = 0;
-    for (int e = 0; e < n_entries && ok; ++e) {
-      const int sp = ctl->ent_span[e];
-      const int span_pos = p.span_pos[sp];
-      const int span_end = span_pos + p.span_len[sp];
-      for (int t = 0; t < ctl->ent_count[e] && ok; ++t, ++j) {
-        const int kt0 = span_pos + (ctl->ent_first[e] + t) * kTile;
-        ok = mbar_wait(&ctl->s_ready, j & 1, err, kErrWaitSoftmax);
+    TileCursor cur;
+    cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (tile_active(geom, w, cur, p.n_sink)) {
+        const int kt0 = cur.kt0;
+        const int span_end = cur.kt_last + 1;
+        ok = mbar_wait(&ctl->s_ready[w], n_done & 1, err, kErrWaitSoftmax);
         ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the TMEM accesses
         if (!ok) break;
         tc_fence_after();
-        const bool my_mask = !(kt0 >= lo && kt0 + kTile - 1 <= hi && kt0 + kTile - 1 < span_end);
-        const bool masked = __any_sync(0xffffffffu, my_mask);
-
-        // pass 1: row maximum of the raw scores
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tS + lane_off + c * 32, r);
-          tmem_ld_wait();
-          if (masked) {
+        uint32_t r[128];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int tk = kt0 + c * 32 + i;
-              const bool vis = tk <= hi && tk < span_end && (tk >= lo || (tk >= s_p && tk < sink_end));
-              mx = fmaxf(mx, vis ? __uint_as_float(r[i]) : -INFINITY);
-            }
-          } else {
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+        tmem_ld_wait();
+        const bool my_mask = !(kt0 >= lo && kt0 + kTile - 1 <= hi && span_end == kt0 + kTile);
+        if (__any_sync(0xffffffffu, my_mask)) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 128; ++i) {
+            if (!key_visible(kt0 + i, lo, hi, s_p, sink_end, span_end)) r[i] = 0xff800000u;  // -inf
           }
         }
-        // Lazy rescale: keep the old reference maximum unless the new one exceeds it by more
-        // than 2^8, so that O in TMEM is only touched rarely.
-        const float mt = mx * sl2;
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 128; i += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(r[i]));
+          mx1 = fmaxf(mx1, __uint_as_float(r[i + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(r[i + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(r[i + 3]));
+        }
+        // Lazy rescale: keep the old reference maximum unless the new one exceeds it by more than
+        // 2^8, so that O in TMEM is only touched rarely.
+        const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
         float alpha = 1.f;
         const bool grow = mt > m_ref + 8.f;
         if (grow) {
           alpha = ex2f(m_ref - mt);  // 0 when m_ref is -inf
           m_ref = mt;
         }
-        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        if (n_done > 0 && __any_sync(0xffffffffu, grow)) {
+          // O_w must be at rest: wait for the product of the previous tile
+          ok = mbar_wait(&ctl->pv_done[w], (n_done - 1) & 1, err, kErrWaitSoftmax);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
           l_sum *= alpha;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tO + lane_off + c * 32, r);
+            uint32_t o[32];
+            tmem_ld32(tO + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tO + lane_off + c * 32, r);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(tO + c * 32, o);
           }
           tmem_st_wait();
         }
         const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-
-        // pass 2: P = exp2(S * scale_log2 - m), row sum, write P (16-bit) over S
-#pragma unroll 1
+        float l0 = 0.f, l1 = 0.f;
+#pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tS + lane_off + c * 32, r);
-          tmem_ld_wait();
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
-            if (masked) {
-              const int tk = kt0 + c * 32 + i;
-              const bool v0 = tk <= hi && tk < span_end && (tk >= lo || (tk >= s_p && tk < sink_end));
-              const bool v1 = tk + 1 <= hi && tk + 1 < span_end &&
-                              (tk + 1 >= lo || (tk + 1 >= s_p && tk + 1 < sink_end));
-              s0 = v0 ? s0 : -INFINITY;
-              s1 = v1 ? s1 : -INFINITY;
-            }
-            const float e0 = ex2f(fmaf(s0, sl2, -m_use));
-            const float e1 = ex2f(fmaf(s1, sl2, -m_use));
-            l_sum += e0 + e1;
+            const float e0 = ex2f(fmaf(__uint_as_float(r[c * 32 + i]), sl2, -m_use));
+            const float e1 = ex2f(fmaf(__uint_as_float(r[c * 32 + i + 1]), sl2, -m_use));
+            l0 += e0;
+            l1 += e1;
             pk[i >> 1] = pack2<kBf16>(e0, e1);
           }
-          tmem_st16(tS + lane_off + c * 16, pk);
+          tmem_st16(tS + c * 16, pk);
         }
+        l_sum += l0 + l1;
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&ctl->p_ready);
+        mbar_arrive(&ctl->p_ready[w]);
+        ++n_done;
       }
+      cursor_next<kTile>(geom, p.span_pos, p.span_len, cur, j + 1 < n_tiles);
     }
 
     // epilogue: O / l -> out, lse
-    if (ok && n_tiles > 0) ok = mbar_wait(&ctl->pv_done, (n_tiles - 1) & 1, err, kErrWaitEpilogue);
+    if (ok && n_done > 0) ok = mbar_wait(&ctl->pv_done[w], (n_done - 1) & 1, err, kErrWaitEpilogue);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
-    const bool has = ok && n_tiles > 0 && l_sum > 0.f;
+    const bool has = ok && n_done > 0 && l_sum > 0.f;
     const float inv = has ? 1.f / l_sum : 0.f;
-    uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + b * p.o_sb +
-                     static_cast<long long>(row0 + row) * p.o_st + h * p.o_sh;
+    const int grow_q = (tile0 + w) * kTile + row;  // row inside the local q tensor
+    uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<long long>(grow_q) * p.o_st +
+                     h * p.o_sh;
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
-      uint32_t r[32];
-      if (n_tiles > 0 && ok) {
-        tmem_ld32(tO + lane_off + c * 32, r);
+      uint32_t o[32];
+      if (n_done > 0 && ok) {
+        tmem_ld32(tO + c * 32, o);
         tmem_ld_wait();
       }
       if (valid) {
         uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          uint4 o;
+          uint4 q4 = make_uint4(0, 0, 0, 0);
           if (has) {
-            o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]) * inv, __uint_as_float(r[v * 8 + 1]) * inv);
-            o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]) * inv, __uint_as_float(r[v * 8 + 3]) * inv);
-            o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]) * inv, __uint_as_float(r[v * 8 + 5]) * inv);
-            o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]) * inv, __uint_as_float(r[v * 8 + 7]) * inv);
-          } else {
-            o = make_uint4(0, 0, 0, 0);
+            q4.x = pack2<kBf16>(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
+            q4.y = pack2<kBf16>(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
+            q4.z = pack2<kBf16>(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
+            q4.w = pack2<kBf16>(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
           }
-          dst[v] = o;
+          dst[v] = q4;
         }
       }
     }
     if (valid) {
-      p.lse[b * p.l_sb + h * p.l_sh + row0 + row] =
-          has ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+      p.lse[b * p.l_sb + h * p.l_sh + grow_q] = has ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
     }
   }
 
@@ -348,7 +349,7 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
 }  // namespace
 
 int launch_fwd(const FwdKernelParams& kp, int dtype, cudaStream_t stream) {
-  const long long n_cta = static_cast<long long>(kp.n_q_tiles) * kp.hq * kp.batch;
+  const long long n_cta = static_cast<long long>((kp.n_q_tiles + 1) / 2) * kp.hq * kp.batch;
   if (n_cta <= 0) return RSWA_OK;
   if (n_cta > 0x7fffffffLL) {
     set_error("rswa_fwd: too many query tiles (%lld)", n_cta);

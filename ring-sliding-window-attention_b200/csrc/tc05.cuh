@@ -13,6 +13,9 @@ namespace tc05 {
 #ifndef RSWA_SPIN_LIMIT
 #define RSWA_SPIN_LIMIT (1u << 24)
 #endif
+#ifndef RSWA_WAIT_LIMIT_NS
+#define RSWA_WAIT_LIMIT_NS 200000000ull /* 0.2 s per wait */
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -56,9 +59,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // thread of the CTA has already raised the flag, so that every role unwinds together.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err_flag,
                                           int code) {
+  // Two limits: a poll count and wall time (try_wait may itself suspend the thread for a while, so
+  // the poll count alone does not bound the time).
+  uint64_t t_start = 0;
   for (uint32_t i = 0; i < RSWA_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *err_flag != 0) return false;
+    if ((i & 255u) == 255u) {
+      if (*err_flag != 0) return false;
+      uint64_t now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t_start == 0) t_start = now;
+      else if (now - t_start > RSWA_WAIT_LIMIT_NS) break;
+    }
   }
   if (*err_flag == 0) *err_flag = code;
   return false;
