@@ -29,12 +29,13 @@ using namespace tc05;
 
 namespace {
 
-constexpr int kFwdThreads = 384;   // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-7 / 8-11 softmax
+constexpr int kFwdThreads = 384;   // warp 0 TMA, warps 1-2 MMA (one per query tile), warp 3 idle, warps 4-7 / 8-11 softmax
 constexpr int kFwdTmemCols = 512;
-constexpr int kFwdSmemTiles = 6 * kTileBytes;  // Q_0, Q_1, K x 2, V x 2
+constexpr int kFwdSmemTiles = 7 * kTileBytes;  // Q_0, Q_1, K x 3, V x 2
+constexpr int kKStages = 3;
 
 struct FwdCtl {
-  uint64_t q_full, k_full[2], v_full[2], k_free[2], v_free[2], s_ready[2], p_ready[2], pv_done[2];
+  uint64_t q_full, k_full[kKStages], v_full[2], k_free[kKStages], v_free[2], s_ready[2], p_ready[2], pv_done[2];
   uint32_t tmem_base;
   int err;
   QBlockGeom geom;
@@ -54,8 +55,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;                     // two query tiles
-  uint8_t* sK = smem + 2 * kTileBytes;    // two stages
-  uint8_t* sV = smem + 4 * kTileBytes;    // two stages
+  uint8_t* sK = smem + 2 * kTileBytes;    // three stages (K is consumed one key tile ahead of V)
+  uint8_t* sV = smem + 5 * kTileBytes;    // two stages
   FwdCtl* ctl = reinterpret_cast<FwdCtl*>(smem + kFwdSmemTiles);
   QBlockGeom* geom = &ctl->geom;
 
@@ -77,11 +78,13 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < kKStages; ++i) {
       mbar_init(&ctl->k_full[i], 1);
+      mbar_init(&ctl->k_free[i], 2);  // both MMA issuers release a stage
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&ctl->v_full[i], 1);
-      mbar_init(&ctl->k_free[i], 1);
-      mbar_init(&ctl->v_free[i], 1);
+      mbar_init(&ctl->v_free[i], 2);
       mbar_init(&ctl->s_ready[i], 1);
       mbar_init(&ctl->p_ready[i], 128);
       mbar_init(&ctl->pv_done[i], 1);
@@ -104,7 +107,7 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   const int n_tiles = (ctl->err != 0) ? 0 : geom->n_tiles;
 
   if (warp < 4) {
-    setmaxnreg_dec<48>();
+    setmaxnreg_dec<64>();
     if (warp == 0 && lane == 0 && n_tiles > 0) {
       // ------------------------------------------------------------------ TMA producer
       const bool two = geom->n_valid[1] > 0;
@@ -119,12 +122,12 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       cursor_begin<kTile>(geom, p.span_pos, p.span_len, c);
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j & 1;
-        if (j >= 2) ok = mbar_wait(&ctl->k_free[st], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
+        const int st = j & 1, sk = j % kKStages;
+        if (j >= kKStages) ok = mbar_wait(&ctl->k_free[sk], ((j / kKStages) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
-        mbar_expect_tx(&ctl->k_full[st], kTileBytes);
-        tma_load_4d(sK + st * kTileBytes, &p.k_map[c.span], &ctl->k_full[st], 0, hk, c.tok, b);
-        tma_load_4d(sK + st * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[st], 64, hk, c.tok, b);
+        mbar_expect_tx(&ctl->k_full[sk], kTileBytes);
+        tma_load_4d(sK + sk * kTileBytes, &p.k_map[c.span], &ctl->k_full[sk], 0, hk, c.tok, b);
+        tma_load_4d(sK + sk * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[sk], 64, hk, c.tok, b);
         if (j >= 2) ok = mbar_wait(&ctl->v_free[st], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
         mbar_expect_tx(&ctl->v_full[st], kTileBytes);
@@ -132,67 +135,66 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
         tma_load_4d(sV + st * kTileBytes + kBoxBytes, &p.v_map[c.span], &ctl->v_full[st], 64, hk, c.tok, b);
         cursor_next<kTile>(geom, p.span_pos, p.span_len, c, j + 1 < n_tiles);
       }
-    } else if (warp == 1 && lane == 0 && n_tiles > 0) {
-      // ------------------------------------------------------------------ MMA issuer
+    } else if ((warp == 1 || warp == 2) && lane == 0 && n_tiles > 0) {
+      // ------------------------------------------------------------------ MMA issuers
+      // One issuing thread per query tile (warps 1 and 2): the two instruction streams are independent
+      // (different accumulators) and issuing them from two warps halves the issue cost per product.
+      const int w = warp - 1;
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t idesc_pv = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
-      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
-      int n_pv[2] = {0, 0};  // products O_w += P_w V issued so far (also the phase of p_ready[w])
+      // descriptors are built once; per stage / k-step only their address field moves (16-byte units)
+      constexpr uint32_t kTile16 = kTileBytes >> 4;
+      const uint64_t dQ = smem_desc_sw128(smem_u32(sQ) + w * kTileBytes, 16, 1024);
+      const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t dV = smem_desc_sw128(smem_u32(sV), kBoxBytes, 1024);
+      const uint32_t tSw = tmem + 128 * w, tOw = tmem + 256 + 128 * w;
+      int n_pv = 0;  // products O_w += P_w V issued so far (also the phase of p_ready[w])
       TileCursor cur, nxt;
       cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
       bool ok = mbar_wait(&ctl->q_full, 0, err, kErrWaitMma);
       if (ok) ok = mbar_wait(&ctl->k_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
+        if (tile_active(geom, w, cur, p.n_sink)) {
 #pragma unroll
-        for (int w = 0; w < 2; ++w) {
-          if (tile_active(geom, w, cur, p.n_sink)) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-              mma_ss(tmem + 128 * w, smem_desc_sw128(aQ + w * kTileBytes + off, 16, 1024),
-                     smem_desc_sw128(aK + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
-            }
-            mma_commit(&ctl->s_ready[w]);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+            mma_ss(tSw, dQ + off, dK + off, idesc_qk, k > 0 ? 1u : 0u);
           }
+          mma_commit(&ctl->s_ready[w]);
         }
         mma_commit(&ctl->k_free[0]);
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
         const bool more = j + 1 < n_tiles;
-        const int sv = j & 1, sk = (j + 1) & 1;
+        const int sv = j & 1, sk = (j + 1) % kKStages;
         nxt = cur;
         cursor_next<kTile>(geom, p.span_pos, p.span_len, nxt, more);
         ok = mbar_wait(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
-        if (ok && more) ok = mbar_wait(&ctl->k_full[sk], ((j + 1) >> 1) & 1, err, kErrWaitMma);
+        if (ok && more) ok = mbar_wait(&ctl->k_full[sk], ((j + 1) / kKStages) & 1, err, kErrWaitMma);
         if (!ok) break;
+        if (tile_active(geom, w, cur, p.n_sink)) {
+          ok = mbar_wait(&ctl->p_ready[w], n_pv & 1, err, kErrWaitMma);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t dVs = dV + sv * kTile16;
 #pragma unroll
-        for (int w = 0; w < 2; ++w) {
-          if (tile_active(geom, w, cur, p.n_sink)) {
-            ok = mbar_wait(&ctl->p_ready[w], n_pv[w] & 1, err, kErrWaitMma);
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              mma_ts(tmem + 256 + 128 * w, tmem + 128 * w + k * 8,
-                     smem_desc_sw128(aV + sv * kTileBytes + k * 2048, kBoxBytes, 1024), idesc_pv,
-                     (n_pv[w] > 0 || k > 0) ? 1u : 0u);
-            }
-            mma_commit(&ctl->pv_done[w]);
-            ++n_pv[w];
+          for (int k = 0; k < 8; ++k) {
+            mma_ts(tOw, tSw + k * 8, dVs + k * 128, idesc_pv, (n_pv > 0 || k > 0) ? 1u : 0u);
           }
-          if (more && tile_active(geom, w, nxt, p.n_sink)) {
-            // overwrites P_w of the current tile: ordered behind the product just issued
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-              mma_ss(tmem + 128 * w, smem_desc_sw128(aQ + w * kTileBytes + off, 16, 1024),
-                     smem_desc_sw128(aK + sk * kTileBytes + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
-            }
-            mma_commit(&ctl->s_ready[w]);
-          }
+          mma_commit(&ctl->pv_done[w]);
+          ++n_pv;
         }
-        if (!ok) break;
+        if (more && tile_active(geom, w, nxt, p.n_sink)) {
+          // overwrites P_w of the current tile: ordered behind the product just issued
+          const uint64_t dKs = dK + sk * kTile16;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+            mma_ss(tSw, dQ + off, dKs + off, idesc_qk, k > 0 ? 1u : 0u);
+          }
+          mma_commit(&ctl->s_ready[w]);
+        }
         mma_commit(&ctl->v_free[sv]);
         if (more) mma_commit(&ctl->k_free[sk]);
         cur = nxt;
@@ -200,7 +202,7 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
     }
   } else {
     // -------------------------------------------------------------------- softmax warp groups
-    setmaxnreg_inc<224>();  // 128 x 48 + 256 x 224 <= 384 x 168 (the launch allocation)
+    setmaxnreg_inc<216>();  // 128 x 64 + 256 x 216 <= 384 x 168 (the launch allocation)
     const int w = (warp - 4) >> 2;          // query tile of the block this warp group owns
     const int quad = warp & 3;              // TMEM lane quadrant this warp may touch
     const int row = quad * 32 + lane;       // query row inside the tile

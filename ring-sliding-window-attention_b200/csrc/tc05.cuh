@@ -196,6 +196,39 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
       : "memory");
 }
 
+// Warp-converged variants: the whole warp executes the call with identical arguments and one
+// elected lane issues the instruction.  Keeping the surrounding control flow and descriptor
+// arithmetic warp-uniform makes the issue path much cheaper than a lane-0-only region.
+__device__ __forceinline__ void mma_ss_w(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_w(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(smem_u32(bar))
+      : "memory");
+}
+// Bounded wait by a whole warp: every lane polls, the result is made uniform.
+__device__ __forceinline__ bool mbar_wait_w(uint64_t* bar, uint32_t parity, volatile int* err_flag, int code) {
+  const bool ok = mbar_wait(bar, parity, err_flag, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ---------------------------------------------------------------- TMEM <-> registers
 // 32 lanes x 32-bit, N consecutive columns per thread: thread i of the warp owns lane
 // (warp%4)*32 + i.  The address carries the lane in bits 31..16 and the column in bits 15..0.
