@@ -6,7 +6,7 @@ each hop's mask case discard what is not visible.  Here every rank works out, fr
 inputs, exactly which trailing tokens of which earlier rank it can see, and only those travel:
 rank r needs the keys at global positions [max(seq_start, r*S - W), r*S), i.e. the trailing
 min(S, ...) tokens of ranks r-1, r-2, ..., plus (StreamingLLM) the first n_sink tokens of the
-sequence that crosses its left edge when those lie further back
+sequence that crosses its left edge, sent by the rank that owns them
 (ring_swa/streaming_llm/nonvarlen.py:48-55 broadcasts them from group rank 0).
 """
 from __future__ import annotations
@@ -80,10 +80,23 @@ def seq_start_of(pos: int, cu: Optional[Sequence[int]]) -> int:
 
 
 def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv], Optional[SinkRecv]]:
-    """What rank r must receive: (lowest needed window position, halos, sink)."""
+    """What rank r must receive: (lowest needed window position, halos, sink).
+
+    The sink tokens of the sequence that crosses the rank's left edge always travel as their own
+    small message when they live on an earlier rank, even if the window reaches them: every query
+    of that sequence needs them, also the ones that otherwise see local keys only and run before
+    the halo has arrived.  The halo then starts behind the sink tokens, so the two never overlap.
+    """
     left = r * S
     s_cross = seq_start_of(left, cu)
     lo = max(s_cross, left - W, 0)
+    sink = None
+    if n_sink > 0 and s_cross < left:
+        owner = s_cross // S
+        end = min(s_cross + n_sink, left, (owner + 1) * S)
+        if end > s_cross:
+            sink = SinkRecv(owner=owner, pos_start=s_cross, n=end - s_cross)
+            lo = max(lo, end)
     halos: List[HaloRecv] = []
     h = 1
     while r - h >= 0:
@@ -93,12 +106,6 @@ def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv]
         start = max(lo, a)
         halos.append(HaloRecv(hop=h, src=r - h, length=b - start, pos_start=start))
         h += 1
-    sink = None
-    if n_sink > 0 and s_cross < lo:
-        owner = s_cross // S
-        end = min(s_cross + n_sink, lo, (owner + 1) * S)
-        if end > s_cross:
-            sink = SinkRecv(owner=owner, pos_start=s_cross, n=end - s_cross)
     return lo, halos, sink
 
 

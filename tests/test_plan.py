@@ -48,13 +48,23 @@ def test_varlen_halo_stops_at_sequence_start():
     assert p.halo_recv == [] and p.halo_tile_end == 0
 
 
-def test_sink_only_when_out_of_reach():
+def test_sink_travels_separately_and_never_overlaps_the_halo():
     p = make_plan(4, 3, 16, 5, 1, None)
-    assert p.sink_recv is not None and (p.sink_recv.owner, p.sink_recv.pos_start, p.sink_recv.n) == (0, 0, 1)
-    p = make_plan(4, 1, 16, 20, 1, None)     # window reaches token 0: no separate sink
-    assert p.sink_recv is None
-    p = make_plan(4, 1, 16, 14, 4, None)     # window reaches position 2: sinks 0 and 1 travel
-    assert (p.sink_recv.pos_start, p.sink_recv.n) == (0, 2)
+    assert (p.sink_recv.owner, p.sink_recv.pos_start, p.sink_recv.n) == (0, 0, 1)
+    # window reaches token 0: the sink still has its own message and the halo starts behind it
+    p = make_plan(4, 1, 16, 20, 1, None)
+    assert (p.sink_recv.pos_start, p.sink_recv.n) == (0, 1)
+    assert [(h.pos_start, h.length) for h in p.halo_recv] == [(1, 15)]
+    p = make_plan(4, 1, 16, 14, 4, None)
+    assert (p.sink_recv.pos_start, p.sink_recv.n) == (0, 4)
+    assert [(h.pos_start, h.length) for h in p.halo_recv] == [(4, 12)]
+    # the sequence starts on this rank: its sink is local, nothing extra travels
+    assert make_plan(4, 2, 16, 5, 1, [0, 32, 64]).sink_recv is None
+    assert make_plan(4, 0, 16, 5, 1, None).sink_recv is None
+    # packed: the crossing sequence starts inside the window's reach on the previous rank
+    p = make_plan(2, 1, 300, 50, 1, [0, 280, 600])
+    assert (p.sink_recv.owner, p.sink_recv.pos_start, p.sink_recv.n) == (0, 280, 1)
+    assert [(h.pos_start, h.length) for h in p.halo_recv] == [(281, 19)]
 
 
 def test_rejects_bad_geometry():

@@ -78,6 +78,10 @@ def test_ring_matches_dense_oracle_cp2():
         _dense_job("ring_sliding_window_attn_varlen", 600, None, 2, 1, 8, 400, 19, cu=[0, 10, 600]),
         _dense_job("ring_streaming_llm_attn_varlen", 600, None, 2, 1, 8, 50, 20, cu=[0, 130, 500, 600], n_sink=1),
         _dense_job("ring_streaming_llm_attn_varlen", 600, None, 2, 2, 8, 50, 21, cu=[0, 130, 500, 600], n_sink=2),
+        # the sink of the crossing sequence lies inside the window's reach on the previous rank, while the
+        # later query tiles of this rank run before the halo arrives
+        _dense_job("ring_streaming_llm_attn_varlen", 600, None, 2, 1, 8, 50, 22, cu=[0, 280, 600], n_sink=1),
+        _dense_job("ring_streaming_llm_attn", 600, 1, 2, 1, 8, 400, 23, n_sink=2),
     ]
     res = _spawn(2, 29741, jobs)
     _assert_small(res, jobs, TOL)
