@@ -37,8 +37,8 @@ extern "C" {
 #define RSWA_NOALLOC_SCRATCH_BYTES (64ll << 20)
 
 /* bits of rswa_bwd_params_t.flags */
-#define RSWA_BWD_INIT 1   /* compute delta = rowsum(dO*O) and zero the fp32 dQ accumulator */
-#define RSWA_BWD_FINISH 2 /* scale + convert the fp32 dQ accumulator into dq */
+#define RSWA_BWD_INIT 1   /* fill the workspace rows: delta = rowsum(dO*O) and lse*log2(e) */
+#define RSWA_BWD_FINISH 2 /* also compute dq, summed over ALL spans of this call */
 
 /* A span is a run of consecutive tokens' K and V (and, in backward, their gradients) that sits
  * in one buffer: the rank's own tokens, a halo received from an earlier rank, or the sink
@@ -95,10 +95,14 @@ typedef struct rswa_fwd_params {
 int rswa_fwd(const rswa_fwd_params_t* p, void* stream);
 
 /* Backward: dq [batch,q_len,Hq,D] and per-span dk/dv from (dO, q, spans, out, lse), using the
- * final (merged) out and lse.  `workspace` is rswa_bwd_workspace_bytes() of device memory: the
- * fp32 dQ accumulator and the fp32 delta rows.  One call with flags INIT|FINISH does a whole
- * backward; a ring rank calls it once per group of spans (INIT on the first, FINISH on the last)
- * with the same workspace so that dQ accumulates across them.
+ * final (merged) out and lse.  Two kernels: a key-stationary one writes dk/dv of every span that
+ * carries dk/dv pointers (spans with both NULL take part in dq only), a query-stationary one
+ * writes dq summed over all spans of the call when FINISH is set.  Nothing is reduced through
+ * global memory, so the result is deterministic.  `workspace` is rswa_bwd_workspace_bytes() of
+ * device memory (two fp32 rows per batch row and head: delta and the scaled lse, filled by INIT).
+ * One call with flags INIT|FINISH does a whole backward.  A ring rank calls it twice with the same
+ * workspace: INIT with the received spans only (their gradients can leave early), then FINISH with
+ * every span, gradient pointers on the local one only.
  * Replaces wrapped_flash_attn_bwd / wrapped_flash_attn_bwd_varlen
  * (ring_swa/ops/wrap_flash.py:276-327, 330-429) and ring_swa/ops/attn.py:63-126. */
 typedef struct rswa_bwd_params {
@@ -118,7 +122,7 @@ typedef struct rswa_bwd_params {
   int32_t flags;
   int32_t* status;
   /* Optional profiling hooks: events from rswa_event_create(), recorded on the stream right
-   * before and right after the main backward kernel (the delta and convert kernels excluded).
+   * before and right after the two tensor-core kernels (the delta kernel excluded).
    * NULL to skip. */
   void* ev_main_start;
   void* ev_main_stop;
@@ -129,18 +133,18 @@ int rswa_bwd(const rswa_bwd_params_t* p, void* stream);
 
 /* The whole backward for callers that cannot allocate device memory: same inputs, outputs and
  * result as rswa_bwd with flags INIT|FINISH, but `workspace`, `workspace_bytes` and `flags` are
- * ignored.  The scratch (fp32 dQ accumulator + delta rows) is a fixed array of
+ * ignored.  The scratch (the delta and scaled-lse rows the kernels read) is a fixed array of
  * RSWA_NOALLOC_SCRATCH_BYTES that is part of the library's device image, so every GPU that loads
  * the library carries it until the process exits, and the call itself never allocates or frees.
  * Meant for hosts that are handed only the operator's tensors (a plugin inside another runtime),
  * that gave away all device memory at start-up, or that must not stall their other streams with
  * the device-wide synchronisation an allocation implies.
  *  - rswa_bwd_workspace_bytes(batch, q_len, n_q_heads, 128) must not exceed
- *    RSWA_NOALLOC_SCRATCH_BYTES (about batch*q_len*n_q_heads <= 130000 rows, e.g. 4096 tokens of
+ *    RSWA_NOALLOC_SCRATCH_BYTES (batch*n_q_heads*q_len <= about 8 million rows, e.g. 262144 tokens of
  *    32 heads); larger problems return RSWA_E_NOALLOC_SIZE and launch nothing.
  *  - The first call on each device looks the array's device address up (with that device
  *    current).  Make that first call outside any stream capture.
- *  - All calls on a device share the array: it is re-initialised at the start of each call, and
+ *  - All calls on a device share the array: it is rewritten at the start of each call, and
  *    two calls that can overlap on the GPU (different streams, no dependency) corrupt each other.
  * Has no counterpart in the reference, whose backward allocates its accumulators with torch on
  * every call (ring_swa/sliding_window/nonvarlen.py:192-195). */

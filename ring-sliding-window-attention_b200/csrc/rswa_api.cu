@@ -10,7 +10,7 @@ namespace rswa {
 int launch_fwd(const FwdKernelParams& kp, int dtype, cudaStream_t stream);
 int launch_bwd(const BwdKernelParams& kp, int dtype, int total_key_tiles, cudaStream_t stream);
 int launch_delta(const rswa_bwd_params_t& p, float* delta, float* lse2, int q_len_pad, cudaStream_t stream);
-int launch_dq_convert(const rswa_bwd_params_t& p, const float* dq_acc, cudaStream_t stream);
+int launch_dq(const BwdKernelParams& kp, int dtype, cudaStream_t stream);
 
 static thread_local char g_err[512] = "";
 
@@ -213,9 +213,8 @@ extern "C" int rswa_fwd(const rswa_fwd_params_t* p, void* stream) {
 extern "C" int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_t n_q_heads, int32_t head_dim) {
   if (batch <= 0 || q_len <= 0 || n_q_heads <= 0 || head_dim != kHeadDim) return -1;
   const int64_t q_len_pad = (static_cast<int64_t>(q_len) + kTile - 1) / kTile * kTile;
-  const int64_t dq = static_cast<int64_t>(batch) * q_len * n_q_heads * head_dim * 4;
-  const int64_t rows = static_cast<int64_t>(batch) * n_q_heads * q_len_pad * 4;  // delta, and lse * log2(e)
-  return ((dq + 255) / 256) * 256 + 2 * rows;
+  // two fp32 rows per (batch, head): delta = rowsum(dO * O) and lse * log2(e), padded to whole tiles
+  return 2 * static_cast<int64_t>(batch) * n_q_heads * q_len_pad * 4;
 }
 
 extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
@@ -225,10 +224,15 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const rswa_geom_t& g = p->g;
-  int rc = check_geom(g, true);
+  int rc = check_geom(g, false);
   if (rc) return rc;
-  if (!p->q || !p->out || !p->dout || !p->lse || !p->dq || !p->workspace || !p->status) {
-    set_error("rswa_bwd: q, out, dout, lse, dq, workspace and status are required");
+  if (!p->q || !p->out || !p->dout || !p->lse || !p->workspace || !p->status) {
+    set_error("rswa_bwd: q, out, dout, lse, workspace and status are required");
+    return RSWA_E_ARG;
+  }
+  const bool want_dq = (p->flags & RSWA_BWD_FINISH) != 0;
+  if (want_dq && !p->dq) {
+    set_error("rswa_bwd: dq is required with RSWA_BWD_FINISH");
     return RSWA_E_ARG;
   }
   const int64_t need = rswa_bwd_workspace_bytes(g.batch, g.q_len, g.n_q_heads, g.head_dim);
@@ -237,84 +241,94 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
               (long long)p->workspace_bytes);
     return RSWA_E_ARG;
   }
-  if (!aligned16(p->dq) || (p->dq_stride_b % 8) || (p->dq_stride_t % 8) || (p->dq_stride_h % 8) ||
+  if ((want_dq && (!aligned16(p->dq) || (p->dq_stride_b % 8) || (p->dq_stride_t % 8) || (p->dq_stride_h % 8))) ||
       !aligned16(p->out) || (p->o_stride_t % 8) || (p->o_stride_h % 8) || (p->o_stride_b % 8)) {
     set_error("rswa_bwd: dq/out must be 16-byte aligned with strides that are multiples of 8 elements");
     return RSWA_E_ARG;
   }
   const int q_len_pad = (g.q_len + kTile - 1) / kTile * kTile;
-  const int64_t dq_bytes = static_cast<int64_t>(g.batch) * g.q_len * g.n_q_heads * kHeadDim * 4;
-  float* dq_acc = static_cast<float*>(p->workspace);
-  float* delta = reinterpret_cast<float*>(static_cast<char*>(p->workspace) + ((dq_bytes + 255) / 256) * 256);
+  float* delta = static_cast<float*>(p->workspace);
   float* lse2 = delta + static_cast<int64_t>(g.batch) * g.n_q_heads * q_len_pad;
 
-  BwdKernelParams kp;
-  memset(&kp, 0, sizeof(kp));
-  rc = make_tile_map(&kp.q_map, p->q, g.dtype, g.batch, g.q_len, g.n_q_heads, p->q_stride_b, p->q_stride_t,
+  // kq: every span (the dQ kernel sums over all keys); kk: only the spans whose dK/dV are wanted
+  BwdKernelParams kq, kk;
+  memset(&kq, 0, sizeof(kq));
+  rc = make_tile_map(&kq.q_map, p->q, g.dtype, g.batch, g.q_len, g.n_q_heads, p->q_stride_b, p->q_stride_t,
                      p->q_stride_h);
   if (rc) return rc;
-  rc = make_tile_map(&kp.do_map, p->dout, g.dtype, g.batch, g.q_len, g.n_q_heads, p->do_stride_b,
+  rc = make_tile_map(&kq.do_map, p->dout, g.dtype, g.batch, g.q_len, g.n_q_heads, p->do_stride_b,
                      p->do_stride_t, p->do_stride_h);
   if (rc) return rc;
-  rc = fill_span_maps(g, kp.k_map, kp.v_map, kp.span_pos, kp.span_len);
+  rc = fill_span_maps(g, kq.k_map, kq.v_map, kq.span_pos, kq.span_len);
   if (rc) return rc;
-  int total_tiles = 0;
+  kq.n_spans = g.n_spans;
+  kq.batch = g.batch;
+  kq.q_len = g.q_len;
+  kq.hq = g.n_q_heads;
+  kq.hkv = g.n_kv_heads;
+  kq.q_pos_start = g.q_pos_start;
+  kq.window = g.window;
+  kq.n_sink = g.n_sink;
+  kq.scale = g.softmax_scale;
+  kq.scale_log2 = g.softmax_scale * 1.4426950408889634f;
+  kq.cu = g.cu_seqlens;
+  kq.n_seqs = g.n_seqs;
+  kq.lse2 = lse2;
+  kq.delta = delta;
+  kq.d_sb = static_cast<long long>(g.n_q_heads) * q_len_pad;
+  kq.d_sh = q_len_pad;
+  kq.dq = p->dq;
+  kq.dq_sb = p->dq_stride_b;
+  kq.dq_st = p->dq_stride_t;
+  kq.dq_sh = p->dq_stride_h;
+  kq.status = p->status;
+
+  kk = kq;
+  int n_k = 0, total_tiles = 0;
   for (int i = 0; i < g.n_spans; ++i) {
     const rswa_span_t& s = g.spans[i];
-    kp.span_tile0[i] = total_tiles;
-    total_tiles += (s.len + kTile - 1) / kTile;
-    kp.dk[i] = s.dk;
-    kp.dv[i] = s.dv;
-    kp.dkv_sb[i] = s.dkv_stride_b;
-    kp.dkv_st[i] = s.dkv_stride_t;
-    kp.dkv_sh[i] = s.dkv_stride_h;
-    kp.grad_fp32[i] = s.grad_fp32;
+    if (s.dk == nullptr && s.dv == nullptr) continue;  // no gradients wanted for this span in this call
+    if (s.dk == nullptr || s.dv == nullptr) {
+      set_error("rswa_bwd: span %d: dk and dv must be given together", i);
+      return RSWA_E_ARG;
+    }
     const int al = s.grad_fp32 ? 4 : 8;
     if (!aligned16(s.dk) || !aligned16(s.dv) || (s.dkv_stride_b % al) || (s.dkv_stride_t % al) ||
         (s.dkv_stride_h % al)) {
       set_error("rswa_bwd: span %d dk/dv must be 16-byte aligned with 16-byte multiple strides", i);
       return RSWA_E_ARG;
     }
+    kk.k_map[n_k] = kq.k_map[i];
+    kk.v_map[n_k] = kq.v_map[i];
+    kk.span_pos[n_k] = s.pos_start;
+    kk.span_len[n_k] = s.len;
+    kk.span_tile0[n_k] = total_tiles;
+    total_tiles += (s.len + kTile - 1) / kTile;
+    kk.dk[n_k] = s.dk;
+    kk.dv[n_k] = s.dv;
+    kk.dkv_sb[n_k] = s.dkv_stride_b;
+    kk.dkv_st[n_k] = s.dkv_stride_t;
+    kk.dkv_sh[n_k] = s.dkv_stride_h;
+    kk.grad_fp32[n_k] = s.grad_fp32;
+    ++n_k;
   }
-  kp.span_tile0[g.n_spans] = total_tiles;
-  kp.n_spans = g.n_spans;
-  kp.batch = g.batch;
-  kp.q_len = g.q_len;
-  kp.hq = g.n_q_heads;
-  kp.hkv = g.n_kv_heads;
-  kp.q_pos_start = g.q_pos_start;
-  kp.window = g.window;
-  kp.n_sink = g.n_sink;
-  kp.scale = g.softmax_scale;
-  kp.scale_log2 = g.softmax_scale * 1.4426950408889634f;
-  kp.cu = g.cu_seqlens;
-  kp.n_seqs = g.n_seqs;
-  kp.lse2 = lse2;
-  kp.delta = delta;
-  kp.d_sb = static_cast<long long>(g.n_q_heads) * q_len_pad;
-  kp.d_sh = q_len_pad;
-  kp.dq_acc = dq_acc;
-  kp.status = p->status;
+  kk.span_tile0[n_k] = total_tiles;
+  kk.n_spans = n_k;
 
   if (p->flags & RSWA_BWD_INIT) {
-    cudaError_t e = cudaMemsetAsync(dq_acc, 0, dq_bytes, stream);
-    if (e != cudaSuccess) {
-      set_error("rswa_bwd: memset: %s", cudaGetErrorString(e));
-      return RSWA_E_CUDA;
-    }
     rc = launch_delta(*p, delta, lse2, q_len_pad, stream);
     if (rc) return rc;
   }
   if (p->ev_main_start) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream);
   if (total_tiles > 0) {
-    rc = launch_bwd(kp, g.dtype, total_tiles, stream);
+    rc = launch_bwd(kk, g.dtype, total_tiles, stream);
+    if (rc) return rc;
+  }
+  if (want_dq) {
+    rc = launch_dq(kq, g.dtype, stream);
     if (rc) return rc;
   }
   if (p->ev_main_stop) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_stop), stream);
-  if (p->flags & RSWA_BWD_FINISH) {
-    rc = launch_dq_convert(*p, dq_acc, stream);
-    if (rc) return rc;
-  }
   return RSWA_OK;
 }
 

@@ -1,4 +1,4 @@
-// Bandwidth-bound helpers around the attention kernels: delta = rowsum(dO * O), fp32 dQ -> 16-bit,
+// Bandwidth-bound helpers around the attention kernels: delta = rowsum(dO * O) and scaled lse rows,
 // the log-sum-exp merge of two partial results, halo-gradient accumulation and the final cast.
 // All are straight streaming kernels: 16-byte accesses, one warp per 128-element row where rows
 // are involved, grid sized from the data.
@@ -65,28 +65,6 @@ __global__ void delta_kernel(const uint16_t* __restrict__ out, long long o_sb, l
     delta[idx] = s;
     lse2[idx] = t < q_len ? lse[b * l_sb + h * l_sh + t] * 1.4426950408889634f : INFINITY;
   }
-}
-
-// dq = scale * dq_acc, fp32 [b, t, h, 128] contiguous -> 16-bit with strides.  8 elements/thread.
-template <bool kBf16>
-__global__ void dq_convert_kernel(const float* __restrict__ acc, uint16_t* __restrict__ dq, long long sb,
-                                  long long st, long long sh, int q_len, int hq, long long n_vec, float scale) {
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= n_vec) return;
-  const int c = i & 15;  // 16 vectors of 8 per 128-element row
-  const long long row = i >> 4;
-  const int h = row % hq;
-  const long long bt = row / hq;
-  const int t = bt % q_len;
-  const long long b = bt / q_len;
-  const float4 x = reinterpret_cast<const float4*>(acc)[i * 2];
-  const float4 y = reinterpret_cast<const float4*>(acc)[i * 2 + 1];
-  uint4 o;
-  o.x = pack2f<kBf16>(x.x * scale, x.y * scale);
-  o.y = pack2f<kBf16>(x.z * scale, x.w * scale);
-  o.z = pack2f<kBf16>(y.x * scale, y.y * scale);
-  o.w = pack2f<kBf16>(y.z * scale, y.w * scale);
-  *reinterpret_cast<uint4*>(dq + b * sb + t * st + h * sh + c * 8) = o;
 }
 
 // LSE merge.  16 threads per (b, t, h) row, each 8 elements (16 bytes) of both inputs.
@@ -188,17 +166,6 @@ int launch_delta(const rswa_bwd_params_t& p, float* delta, float* lse2, int q_le
       static_cast<const uint16_t*>(p.dout), p.do_stride_b, p.do_stride_t, p.do_stride_h, p.lse, p.lse_stride_b,
       p.lse_stride_h, delta, lse2, g.batch, g.q_len, g.n_q_heads, q_len_pad);
   return check_launch("rswa_bwd(delta)");
-}
-
-int launch_dq_convert(const rswa_bwd_params_t& p, const float* dq_acc, cudaStream_t stream) {
-  const rswa_geom_t& g = p.g;
-  const long long n_vec = static_cast<long long>(g.batch) * g.q_len * g.n_q_heads * 16;
-  const int threads = 256;
-  auto kern = g.dtype == RSWA_DTYPE_BF16 ? dq_convert_kernel<true> : dq_convert_kernel<false>;
-  kern<<<static_cast<unsigned>((n_vec + threads - 1) / threads), threads, 0, stream>>>(
-      dq_acc, static_cast<uint16_t*>(p.dq), p.dq_stride_b, p.dq_stride_t, p.dq_stride_h, g.q_len, g.n_q_heads,
-      n_vec, g.softmax_scale);
-  return check_launch("rswa_bwd(dq convert)");
 }
 
 }  // namespace rswa

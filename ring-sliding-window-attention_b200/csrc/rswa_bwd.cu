@@ -1,29 +1,26 @@
-// Backward kernel: one CTA owns a 128-key tile of one KV head and walks every query tile (and
-// every query head of the group) that can see it.  All five products run on the sm_100a tensor
-// cores with TMEM accumulators, in the transposed (key-major) form so that P and dS can be fed
-// back as the A operand straight from tensor memory:
+// dK/dV kernel: the key-stationary half of the backward pass.
+//
+// One CTA owns a 128-key tile of one KV head and walks every query tile (and every query head of
+// the group) that can see it.  The products run in the transposed (key-major) form so that P and
+// dS feed the next MMA as the A operand straight from tensor memory:
 //
 //   S^T  = K Q^T          A = K   (smem, K-major)     B = Q   (smem, K-major)
 //   dP^T = V dO^T         A = V   (smem, K-major)     B = dO  (smem, K-major)
 //   P^T  = exp2(S^T * scale_log2 - lse2),   dS^T = P^T * (dP^T - delta)      (8 compute warps)
 //   dV  += P^T dO         A = P^T (TMEM)              B = dO  (smem, MN-major)
 //   dK  += dS^T Q         A = dS^T(TMEM)              B = Q   (smem, MN-major)
-//   dQ   = dS K           A = dS^T(smem, MN-major)    B = K   (smem, MN-major)
 //
 // dK and dV stay in TMEM for the whole CTA (summed over the query heads of the group) and are
-// written once; dQ tiles are added into an fp32 accumulator in global memory with vector
-// reductions by a dedicated warp group and converted afterwards.  P is recomputed from the saved
-// log-sum-exp, and delta is rowsum(dO * O), which is what makes a per-span backward against the
-// FINAL out/lse exact (the property the reference's per-hop backward relies on,
-// ring_swa/ops/attn.py:63-126).
+// written once.  dQ is the business of the query-stationary kernel (rswa_dq.cu), so nothing is
+// reduced through global memory.  P is recomputed from the saved log-sum-exp, and delta is
+// rowsum(dO * O), which is what makes a per-span backward against the FINAL out/lse exact (the
+// property the reference's per-hop backward relies on, ring_swa/ops/attn.py:63-126).
 //
-// Roles (16 warps): warp 0 TMA producer, warp 1 MMA issuer, warps 4-11 compute, warps 12-15 dQ
-// reduction.  Registers are re-balanced with setmaxnreg (compute warps get 200).
-//
-// TMEM columns: [0,128) dK, [128,256) dV, [256,384) S^T then P^T | dS^T, [384,512) dP^T then dQ.
-// The MMA thread never waits for its own MMAs: tcgen05.mma instructions of one thread execute in
-// issue order, so S^T of the next query tile may be issued right behind the MMAs that still read
-// P^T / dS^T from the same columns.
+// Pipeline: S^T of the next query tile is issued as soon as the compute warps have read the
+// current one out of TMEM, dP^T of the next tile right behind dV/dK of the current one, so the
+// exponentials of tile i+1 overlap the products of tile i.  Q tiles travel through a 3-stage ring
+// (they are needed one tile ahead), dO tiles through a 2-stage ring.  Two warps issue MMAs.
+// TMEM columns: [0,128) dK, [128,256) dV, [256,384) S^T, [384,512) dP^T then P^T | dS^T.
 #include "rswa_common.cuh"
 #include "tc05.cuh"
 
@@ -32,34 +29,28 @@ using namespace tc05;
 
 namespace {
 
-constexpr int kBwdThreads = 512;
+constexpr int kBwdThreads = 384;  // warp 0 TMA, warps 1-2 MMA, warp 3 idle, warps 4-11 compute
 constexpr int kBwdTmemCols = 512;
 constexpr int kComputeThreads = 256;
-constexpr int kReduceThreads = 128;
+constexpr int kQStages = 3;
 
 struct BwdCtl {
-  uint64_t kv_full, qdo_full[2], stage_free[2], s_ready, dp_ready, pds_ready, mma2_done, dq_done;
+  uint64_t kv_full, q_full[kQStages], q_free[kQStages], do_full[2], do_free[2];
+  uint64_t s_ready, s_loaded, dp_ready, pds_ready, dv_done, done;
   uint32_t tmem_base;
   int err;
   int qt_first, n_qt;
 };
 
-// K, V, 2 x (Q, dO), dS  +  2 stages x (lse2, delta) rows  +  control
+// K, V, 3 x Q, 2 x dO  +  3 lse2 rows + 2 delta rows  +  control
 constexpr int kBwdSmemTiles = 7 * kTileBytes;
 constexpr int kRowBytes = kTile * 4;
-constexpr int kBwdSmemBytes = kBwdSmemTiles + 2 * 2 * kRowBytes + 256;
-constexpr uint32_t kStageTxBytes = 2 * kTileBytes + 2 * kRowBytes;
+constexpr int kBwdSmemBytes = kBwdSmemTiles + (kQStages + 2) * kRowBytes + 256;
+constexpr uint32_t kStageTxBytes = kTileBytes + kRowBytes;
 static_assert(sizeof(BwdCtl) <= 256, "control block too large");
 static_assert(kBwdSmemBytes <= 232448, "shared memory budget");
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
 __device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -67,12 +58,11 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem;
   uint8_t* sV = smem + kTileBytes;
-  uint8_t* sQ = smem + 2 * kTileBytes;   // two stages
-  uint8_t* sDO = smem + 4 * kTileBytes;  // two stages
-  uint8_t* sDS = smem + 6 * kTileBytes;
-  float* sLse = reinterpret_cast<float*>(smem + kBwdSmemTiles);  // [2][128]
-  float* sDelta = sLse + 2 * kTile;                              // [2][128]
-  BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + kBwdSmemTiles + 2 * 2 * kRowBytes);
+  uint8_t* sQ = smem + 2 * kTileBytes;   // three stages
+  uint8_t* sDO = smem + 5 * kTileBytes;  // two stages
+  float* sLse = reinterpret_cast<float*>(smem + kBwdSmemTiles);  // [3][128], travels with Q
+  float* sDelta = sLse + kQStages * kTile;                       // [2][128], travels with dO
+  BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + kBwdSmemTiles + (kQStages + 2) * kRowBytes);
 
   // a device-side error was already reported on this stream: do not pile further time-outs on it
   if (__syncthreads_or(*reinterpret_cast<volatile int*>(p.status) != 0)) return;
@@ -97,15 +87,20 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->kv_full, 1);
-    mbar_init(&ctl->qdo_full[0], 1);
-    mbar_init(&ctl->qdo_full[1], 1);
-    mbar_init(&ctl->stage_free[0], 1);
-    mbar_init(&ctl->stage_free[1], 1);
+    for (int i = 0; i < kQStages; ++i) {
+      mbar_init(&ctl->q_full[i], 1);
+      mbar_init(&ctl->q_free[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctl->do_full[i], 1);
+      mbar_init(&ctl->do_free[i], 1);
+    }
     mbar_init(&ctl->s_ready, 1);
+    mbar_init(&ctl->s_loaded, kComputeThreads);
     mbar_init(&ctl->dp_ready, 1);
     mbar_init(&ctl->pds_ready, kComputeThreads);
-    mbar_init(&ctl->mma2_done, 1);
-    mbar_init(&ctl->dq_done, kReduceThreads);
+    mbar_init(&ctl->dv_done, 1);
+    mbar_init(&ctl->done, 2);
     ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
     mbar_fence_init();
     // query tiles that can see at least one key of this tile
@@ -137,103 +132,139 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   tc_fence_after();
 
   const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tDK = tmem, tDV = tmem + 128, tA = tmem + 256, tB = tmem + 384;
-  const uint32_t tP = tA, tDS = tA + 64;
+  const uint32_t tDK = tmem, tDV = tmem + 128, tS = tmem + 256, tB = tmem + 384;
+  const uint32_t tP = tB, tDS = tB + 64;
   volatile int* err = &ctl->err;
   const int qt_first = ctl->qt_first;
   const int n_qt = (ctl->err != 0) ? 0 : ctl->n_qt;
   const int n_iter = n_qt * group;
+  constexpr uint32_t kTile16 = kTileBytes >> 4;
 
   if (warp < 4) {
-    setmaxnreg_dec<48>();
-    if (warp == 0) {
-      // ---------------------------------------------------------------- TMA producer
-      if (lane == 0 && n_iter > 0) {
-        mbar_expect_tx(&ctl->kv_full, 2 * kTileBytes);
-        tma_load_4d(sK, &p.k_map[sp], &ctl->kv_full, 0, hk, key0, b);
-        tma_load_4d(sK + kBoxBytes, &p.k_map[sp], &ctl->kv_full, 64, hk, key0, b);
-        tma_load_4d(sV, &p.v_map[sp], &ctl->kv_full, 0, hk, key0, b);
-        tma_load_4d(sV + kBoxBytes, &p.v_map[sp], &ctl->kv_full, 64, hk, key0, b);
-        bool ok = true;
-        for (int it = 0; it < n_iter && ok; ++it) {
-          const int st = it & 1;
-          const int h = hk * group + it / n_qt;
-          const int row0 = (qt_first + it % n_qt) * kTile;
-          if (it >= 2) ok = mbar_wait(&ctl->stage_free[st], ((it >> 1) - 1) & 1, err, kErrWaitProducer);
-          if (!ok) break;
-          mbar_expect_tx(&ctl->qdo_full[st], kStageTxBytes);
-          uint8_t* q_dst = sQ + st * kTileBytes;
-          uint8_t* do_dst = sDO + st * kTileBytes;
-          tma_load_4d(q_dst, &p.q_map, &ctl->qdo_full[st], 0, h, row0, b);
-          tma_load_4d(q_dst + kBoxBytes, &p.q_map, &ctl->qdo_full[st], 64, h, row0, b);
-          tma_load_4d(do_dst, &p.do_map, &ctl->qdo_full[st], 0, h, row0, b);
-          tma_load_4d(do_dst + kBoxBytes, &p.do_map, &ctl->qdo_full[st], 64, h, row0, b);
-          const long long roff = b * p.d_sb + h * p.d_sh + row0;
-          bulk_load_1d(sLse + st * kTile, p.lse2 + roff, kRowBytes, &ctl->qdo_full[st]);
-          bulk_load_1d(sDelta + st * kTile, p.delta + roff, kRowBytes, &ctl->qdo_full[st]);
-        }
+    setmaxnreg_dec<64>();
+    if (warp == 0 && lane == 0 && n_iter > 0) {
+      // ------------------------------------------------------------------ TMA producer
+      mbar_expect_tx(&ctl->kv_full, 2 * kTileBytes);
+      tma_load_4d(sK, &p.k_map[sp], &ctl->kv_full, 0, hk, key0, b);
+      tma_load_4d(sK + kBoxBytes, &p.k_map[sp], &ctl->kv_full, 64, hk, key0, b);
+      tma_load_4d(sV, &p.v_map[sp], &ctl->kv_full, 0, hk, key0, b);
+      tma_load_4d(sV + kBoxBytes, &p.v_map[sp], &ctl->kv_full, 64, hk, key0, b);
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int sq = it % kQStages, sd = it & 1;
+        const int h = hk * group + it / n_qt;
+        const int row0 = (qt_first + it % n_qt) * kTile;
+        const long long roff = b * p.d_sb + h * p.d_sh + row0;
+        if (it >= kQStages) ok = mbar_wait(&ctl->q_free[sq], ((it / kQStages) - 1) & 1, err, kErrWaitProducer);
+        if (!ok) break;
+        mbar_expect_tx(&ctl->q_full[sq], kStageTxBytes);
+        tma_load_4d(sQ + sq * kTileBytes, &p.q_map, &ctl->q_full[sq], 0, h, row0, b);
+        tma_load_4d(sQ + sq * kTileBytes + kBoxBytes, &p.q_map, &ctl->q_full[sq], 64, h, row0, b);
+        bulk_load_1d(sLse + sq * kTile, p.lse2 + roff, kRowBytes, &ctl->q_full[sq]);
+        if (it >= 2) ok = mbar_wait(&ctl->do_free[sd], ((it >> 1) - 1) & 1, err, kErrWaitProducer);
+        if (!ok) break;
+        mbar_expect_tx(&ctl->do_full[sd], kStageTxBytes);
+        tma_load_4d(sDO + sd * kTileBytes, &p.do_map, &ctl->do_full[sd], 0, h, row0, b);
+        tma_load_4d(sDO + sd * kTileBytes + kBoxBytes, &p.do_map, &ctl->do_full[sd], 64, h, row0, b);
+        bulk_load_1d(sDelta + sd * kTile, p.delta + roff, kRowBytes, &ctl->do_full[sd]);
       }
-    } else if (warp == 1) {
-      // ---------------------------------------------------------------- MMA issuer
-      if (lane == 0 && n_iter > 0) {
-        constexpr int bf = kBf16 ? 1 : 0;
-        constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);  // both operands K-major
-        constexpr uint32_t id_tn = idesc_f16(128, 128, bf, 0, 1);  // A from TMEM, B MN-major
-        constexpr uint32_t id_nn = idesc_f16(128, 128, bf, 1, 1);  // both MN-major
-        const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
-        bool ok = mbar_wait(&ctl->kv_full, 0, err, kErrWaitMma);
-        for (int it = 0; it < n_iter && ok; ++it) {
-          const int st = it & 1;
-          const uint32_t aQ = smem_u32(sQ + st * kTileBytes), aDO = smem_u32(sDO + st * kTileBytes);
-          ok = mbar_wait(&ctl->qdo_full[st], (it >> 1) & 1, err, kErrWaitMma);
+    } else if (warp == 1 && lane == 0 && n_iter > 0) {
+      // ------------------------------------------------------------------ MMA issuer 1: S^T and dV
+      constexpr int bf = kBf16 ? 1 : 0;
+      constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);  // both operands K-major
+      constexpr uint32_t id_tn = idesc_f16(128, 128, bf, 0, 1);  // A from TMEM, B MN-major
+      const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16, 1024);
+      const uint64_t dQk = smem_desc_sw128(smem_u32(sQ), 16, 1024);
+      const uint64_t dDOm = smem_desc_sw128(smem_u32(sDO), kBoxBytes, 1024);
+      bool ok = mbar_wait(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait(&ctl->q_full[0], 0, err, kErrWaitMma);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+          mma_ss(tS, dK + off, dQk + off, id_kk, k > 0 ? 1u : 0u);
+        }
+        mma_commit(&ctl->s_ready);
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        if (it + 1 < n_iter) {
+          // S^T of the next query tile, once every compute warp holds the current one in registers
+          const int sq = (it + 1) % kQStages;
+          ok = mbar_wait(&ctl->q_full[sq], ((it + 1) / kQStages) & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait(&ctl->s_loaded, it & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
-          // S^T: overwrites the columns P^T / dS^T of the previous tile lived in; the MMAs reading
-          // them were issued earlier by this thread and therefore execute first
+          const uint64_t dQs = dQk + sq * kTile16;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-            mma_ss(tA, smem_desc_sw128(aK + off, 16, 1024), smem_desc_sw128(aQ + off, 16, 1024), id_kk,
-                   k > 0 ? 1u : 0u);
+            const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+            mma_ss(tS, dK + off, dQs + off, id_kk, k > 0 ? 1u : 0u);
           }
           mma_commit(&ctl->s_ready);
-          // dQ of the previous tile lives where dP^T goes: wait until it has been read out
-          if (it > 0) ok = mbar_wait(&ctl->dq_done, (it - 1) & 1, err, kErrWaitMma);
+        }
+        ok = mbar_wait(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t dDOs = dDOm + (it & 1) * kTile16;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // dV += P^T dO
+          mma_ts(tDV, tP + k * 8, dDOs + k * 128, id_tn, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(&ctl->dv_done);
+        mma_commit(&ctl->do_free[it & 1]);
+      }
+      if (ok) mma_commit(&ctl->done);
+    } else if (warp == 2 && lane == 0 && n_iter > 0) {
+      // ------------------------------------------------------------------ MMA issuer 2: dP^T and dK
+      constexpr int bf = kBf16 ? 1 : 0;
+      constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);
+      constexpr uint32_t id_tn = idesc_f16(128, 128, bf, 0, 1);
+      const uint64_t dV = smem_desc_sw128(smem_u32(sV), 16, 1024);
+      const uint64_t dDOk = smem_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t dQm = smem_desc_sw128(smem_u32(sQ), kBoxBytes, 1024);
+      bool ok = mbar_wait(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait(&ctl->do_full[0], 0, err, kErrWaitMma);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+          mma_ss(tB, dV + off, dDOk + off, id_kk, k > 0 ? 1u : 0u);
+        }
+        mma_commit(&ctl->dp_ready);
+      }
+      for (int it = 0; it < n_iter && ok; ++it) {
+        ok = mbar_wait(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t dQs = dQm + (it % kQStages) * kTile16;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // dK += dS^T Q
+          mma_ts(tDK, tDS + k * 8, dQs + k * 128, id_tn, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        mma_commit(&ctl->q_free[it % kQStages]);
+        if (it + 1 < n_iter) {
+          // dP^T of the next tile overwrites P^T | dS^T: behind dK (this thread) and dV (the other)
+          const int sd = (it + 1) & 1;
+          ok = mbar_wait(&ctl->do_full[sd], ((it + 1) >> 1) & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait(&ctl->dv_done, it & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
+          const uint64_t dDOs = dDOk + sd * kTile16;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            const uint32_t off = (k >> 2) * kBoxBytes + (k & 3) * 32;
-            mma_ss(tB, smem_desc_sw128(aV + off, 16, 1024), smem_desc_sw128(aDO + off, 16, 1024), id_kk,
-                   k > 0 ? 1u : 0u);
+            const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+            mma_ss(tB, dV + off, dDOs + off, id_kk, k > 0 ? 1u : 0u);
           }
           mma_commit(&ctl->dp_ready);
-          ok = mbar_wait(&ctl->pds_ready, it & 1, err, kErrWaitMma);
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {  // dV += P^T dO
-            mma_ts(tDV, tP + k * 8, smem_desc_sw128(aDO + k * 2048, kBoxBytes, 1024), id_tn,
-                   (it > 0 || k > 0) ? 1u : 0u);
-          }
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {  // dK += dS^T Q
-            mma_ts(tDK, tDS + k * 8, smem_desc_sw128(aQ + k * 2048, kBoxBytes, 1024), id_tn,
-                   (it > 0 || k > 0) ? 1u : 0u);
-          }
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {  // dQ = dS K
-            mma_ss(tB, smem_desc_sw128(aDS + k * 2048, kBoxBytes, 1024),
-                   smem_desc_sw128(aK + k * 2048, kBoxBytes, 1024), id_nn, k > 0 ? 1u : 0u);
-          }
-          mma_commit(&ctl->mma2_done);
-          mma_commit(&ctl->stage_free[st]);
         }
       }
+      if (ok) mma_commit(&ctl->done);
     }
-  } else if (warp < 12) {
-    // ------------------------------------------------------------------ compute warps
-    setmaxnreg_inc<200>();
+  } else {
+    // -------------------------------------------------------------------- compute warps
+    setmaxnreg_inc<216>();  // 128 x 64 + 256 x 216 <= 384 x 168 (the launch allocation)
     const int quad = warp & 3;
     const int half = (warp - 4) >> 2;            // which 64 query columns this warp handles
     const int row = quad * 32 + lane;            // key row
@@ -249,18 +280,17 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       p_hi = min(p_hi, q_end_pos - 1);
     }
     const float sl2 = p.scale_log2;
-    const uint32_t ds_row = smem_u32(sDS) + half * kBoxBytes + row * 128;
     bool ok = true;
 
     for (int it = 0; it < n_iter && ok; ++it) {
       const int qrow0 = (qt_first + it % n_qt) * kTile;
       const int pq0 = p.q_pos_start + qrow0;
-      const float* lse_s = sLse + (it & 1) * kTile + half * 64;
+      const float* lse_s = sLse + (it % kQStages) * kTile + half * 64;
       const float* del_s = sDelta + (it & 1) * kTile + half * 64;
       const bool full = (pq0 >= t) && (pq0 + kTile - 1 <= p_hi);
       const bool masked = !__all_sync(0xffffffffu, full);
 
-      // P^T from S^T (the lse2 / delta rows of this stage landed before S^T was issued)
+      // P^T from S^T (the lse2 row of this stage landed together with Q, before S^T was issued)
       ok = mbar_wait(&ctl->s_ready, it & 1, err, kErrWaitSoftmax);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -268,9 +298,11 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       float pr[64];
       {
         uint32_t s0[32], s1[32];
-        tmem_ld32(tA + lane_off + half * 64, s0);
-        tmem_ld32(tA + lane_off + half * 64 + 32, s1);
+        tmem_ld32(tS + lane_off + half * 64, s0);
+        tmem_ld32(tS + lane_off + half * 64 + 32, s1);
         tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&ctl->s_loaded);  // S^T of the next query tile may overwrite these columns now
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 la = *reinterpret_cast<const float4*>(lse_s + i);
@@ -321,25 +353,17 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
 #pragma unroll
       for (int i = 0; i < 64; i += 2) ppk[i >> 1] = pack2<kBf16>(pr[i], pr[i + 1]);
       tc_fence_before();
-      bar_sync_compute();  // every compute warp has read its part of S^T and dP^T
+      bar_sync_compute();  // every compute warp has read its part of dP^T: its columns can be reused
       tc_fence_after();
       tmem_st32(tP + lane_off + half * 32, ppk);
       tmem_st32(tDS + lane_off + half * 32, dpk);
-      // dS^T also goes to shared memory ([key][query], query contiguous, 128-byte swizzle) as the
-      // A operand of dQ = dS K
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        st_shared_v4(ds_row + ((c ^ (row & 7)) << 4), dpk[c * 4], dpk[c * 4 + 1], dpk[c * 4 + 2],
-                     dpk[c * 4 + 3]);
-      }
       tmem_st_wait();
-      fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&ctl->pds_ready);
     }
 
     // epilogue: dK (scaled) and dV for this key tile
-    if (ok && n_iter > 0) ok = mbar_wait(&ctl->mma2_done, (n_iter - 1) & 1, err, kErrWaitEpilogue);
+    if (ok && n_iter > 0) ok = mbar_wait(&ctl->done, 0, err, kErrWaitEpilogue);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     if (ok && ctl->err == 0) {
@@ -380,40 +404,6 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
                 dst[v] = o;
               }
             }
-          }
-        }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------------ dQ reduction warps
-    setmaxnreg_dec<64>();
-    const int quad = warp & 3;
-    const int row = quad * 32 + lane;  // query row inside the tile
-    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
-      const int h = hk * group + it / n_qt;
-      const int qrow0 = (qt_first + it % n_qt) * kTile;
-      const bool qv = qrow0 + row < p.q_len;
-      float* dst = p.dq_acc + ((static_cast<long long>(b) * p.q_len + qrow0 + row) * p.hq + h) * kHeadDim;
-      ok = mbar_wait(&ctl->mma2_done, it & 1, err, kErrWaitEpilogue);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tB + lane_off + c * 32, r);
-        tmem_ld_wait();
-        if (c == 3) {  // the whole tile is in registers: the MMA thread may overwrite it
-          tc_fence_before();
-          mbar_arrive(&ctl->dq_done);
-        }
-        if (qv) {
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            red_add_v4(dst + c * 32 + v * 4, __uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
-                       __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
           }
         }
       }

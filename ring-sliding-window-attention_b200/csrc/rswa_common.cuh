@@ -66,7 +66,8 @@ struct BwdKernelParams {
   const float* lse2;
   const float* delta;
   long long d_sb, d_sh;
-  float* dq_acc;  // [batch, q_len, hq, 128] contiguous fp32
+  void* dq;  // [batch, q_len, hq, 128], 16-bit, written by the dQ kernel
+  long long dq_sb, dq_st, dq_sh;
   int* status;
 };
 

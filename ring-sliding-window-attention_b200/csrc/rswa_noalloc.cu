@@ -1,9 +1,10 @@
 // rswa_bwd_noalloc: the whole backward with its scratch memory inside the library.
 //
-// Who this is for.  rswa_bwd needs scratch memory next to its inputs and outputs (the fp32 dQ
-// accumulator that the key-tile CTAs add into, and the delta rows), and leaves it to the caller to
-// allocate it.  Some callers cannot do that at the point where they call us: a plugin that runs
-// inside another runtime's execution phase and is only handed the tensors of the operator, a
+// Who this is for.  rswa_bwd needs scratch memory next to its inputs and outputs (two fp32 rows per
+// batch row and head: delta = rowsum(dO * O) and the scaled log-sum-exp, written by a small kernel
+// and read by both tensor-core kernels), and leaves it to the caller to allocate it.  Some
+// callers cannot do that at the point where they call us: a plugin that runs inside another
+// runtime's execution phase and is only handed the tensors of the operator, a
 // serving process whose device memory was carved up completely at start-up, code that is not
 // allowed to call cudaMalloc because that call synchronises the whole device and would stall the
 // other streams of the process.  For them the scratch lives in a fixed array in this library's
@@ -66,16 +67,16 @@ extern "C" int rswa_bwd_noalloc(const rswa_bwd_params_t* p, void* stream) {
   if (need > RSWA_NOALLOC_SCRATCH_BYTES) {
     rswa::set_error(
         "rswa_bwd_noalloc: this problem needs %lld bytes of scratch, the built-in array holds %lld "
-        "(batch * q_len * n_q_heads must stay below about %lld); use rswa_bwd with a caller-owned workspace",
+        "(batch * n_q_heads * q_len must stay below about %lld); use rswa_bwd with a caller-owned workspace",
         static_cast<long long>(need), static_cast<long long>(RSWA_NOALLOC_SCRATCH_BYTES),
-        static_cast<long long>(RSWA_NOALLOC_SCRATCH_BYTES / (128 * 4 + 4)));
+        static_cast<long long>(RSWA_NOALLOC_SCRATCH_BYTES / 8));
     return RSWA_E_NOALLOC_SIZE;
   }
   void* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);
   if (rc) return rc;
-  // Same work as rswa_bwd over the built-in scratch.  A whole backward in one call: INIT zeroes the
-  // dQ accumulator (the array still holds the previous call's sums) and recomputes delta.
+  // Same work as rswa_bwd over the built-in scratch.  A whole backward in one call: INIT rewrites the
+  // delta and scaled-lse rows (the array still holds the previous call's), FINISH produces dq.
   rswa_bwd_params_t q = *p;
   q.workspace = scratch;
   q.workspace_bytes = RSWA_NOALLOC_SCRATCH_BYTES;

@@ -116,9 +116,9 @@ def _fill_geom(g: _C.Geom, q: torch.Tensor, spans: Sequence[KVSpan], window: int
         c.k, c.v = s.k.data_ptr(), s.v.data_ptr()
         c.kv_stride_b, c.kv_stride_t, c.kv_stride_h = s.k.stride(0), s.k.stride(1), s.k.stride(2)
         c.pos_start, c.len = int(s.pos_start), s.k.shape[1]
-        if grads:
+        if grads and (s.dk is not None or s.dv is not None):
             if s.dk is None or s.dv is None:
-                raise ValueError("backward needs dk and dv for every span")
+                raise ValueError("dk and dv of a span must be given together")
             if s.dk.shape != s.k.shape or s.dv.shape != s.k.shape or s.dk.stride() != s.dv.stride():
                 raise ValueError("dk/dv must match k in shape and each other in strides")
             if s.dk.dtype != s.dv.dtype or s.dk.dtype not in (torch.float32, q.dtype):
@@ -177,7 +177,9 @@ def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.
         dq: torch.Tensor, window: int, n_sink: int, scale: float, q_pos_start: int = 0,
         cu_seqlens: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
         flags: int = _C.BWD_INIT | _C.BWD_FINISH) -> torch.Tensor:
-    """dq and every span's dk/dv.  Returns the workspace so that a later call can continue it."""
+    """K/V gradients of the spans that carry dk/dv buffers, and (with BWD_FINISH) dq summed over ALL given
+    spans.  A ring rank calls it twice: the received spans first (INIT; their gradients leave early), then
+    every span again with gradient buffers on the local one only (FINISH).  Returns the workspace."""
     for name, t in (("q", q), ("out", out), ("dout", dout), ("dq", dq)):
         _check4(name, t)
         if t.dtype != q.dtype or t.shape != q.shape:
@@ -207,7 +209,8 @@ def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.
         bwd_main_events.append((p.ev_main_start, p.ev_main_stop))
     _C.check(_C.lib().rswa_bwd(C.byref(p), _stream()), "rswa_bwd")
     global launch_count
-    launch_count += (1 if flags & _C.BWD_INIT else 0) + (1 if spans else 0) + (1 if flags & _C.BWD_FINISH else 0)
+    launch_count += ((1 if flags & _C.BWD_INIT else 0) + (1 if any(s.dk is not None for s in spans) else 0) +
+                     (1 if flags & _C.BWD_FINISH else 0))
     return workspace
 
 

@@ -202,8 +202,11 @@ class RingAttn(torch.autograd.Function):
         else:
             acc = None
             local = K.KVSpan(k4, v4, plan.q_pos_start, dk=dk4, dv=dv4)
+        # second call: dK/dV of the local span, and dQ over every span (the received ones without
+        # gradient buffers, their gradients are already on the wire)
+        seen = [K.KVSpan(s.k, s.v, s.pos_start) for s in remote]
         flags = _C.BWD_FINISH | (0 if remote else _C.BWD_INIT)
-        K.bwd(q4, [local], out, lse, do4, dq4, workspace=ws, flags=flags, **args)
+        K.bwd(q4, seen + [local], out, lse, do4, dq4, workspace=ws, flags=flags, **args)
         _wait(works)
         if acc is not None:
             for off, n, g in recvs:

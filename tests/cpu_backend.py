@@ -44,16 +44,16 @@ def fwd(q, spans, window, n_sink, scale, q_pos_start=0, cu_seqlens=None, out=Non
 
 
 def bwd_workspace(q):
-    return torch.zeros(q.shape, dtype=torch.float32)
+    return torch.zeros(1, dtype=torch.float32)
 
 
 def bwd(q, spans, out, lse, dout, dq, window, n_sink, scale, q_pos_start=0, cu_seqlens=None, workspace=None,
         flags=3):
+    """dk/dv of the spans that carry gradient buffers; with FINISH, dq over all the spans given."""
     if workspace is None:
         workspace = bwd_workspace(q)
-    if flags & 1:
-        workspace.zero_()
     B, S, Hq, D = q.shape
+    dq_sum = torch.zeros(q.shape, dtype=torch.float32)
     if spans:
         k, v, pos = _cat(spans)
         g = Hq // k.shape[2]
@@ -68,17 +68,18 @@ def bwd(q, spans, out, lse, dout, dq, window, n_sink, scale, q_pos_start=0, cu_s
         dp = torch.einsum("bihd,bjhd->bhij", dof, vr)
         delta = (dof * out.float()).sum(-1).permute(0, 2, 1)
         ds = p * (dp - delta[..., None])
-        workspace += torch.einsum("bhij,bjhd->bihd", ds, kr) * scale
+        dq_sum = torch.einsum("bhij,bjhd->bihd", ds, kr) * scale
         dk = (torch.einsum("bhij,bihd->bjhd", ds, q.float()) * scale).reshape(B, -1, k.shape[2], g, D).sum(3)
         dv = torch.einsum("bhij,bihd->bjhd", p, dof).reshape(B, -1, k.shape[2], g, D).sum(3)
         off = 0
         for sp in spans:
             n = sp.k.shape[1]
-            sp.dk.copy_(dk[:, off:off + n].to(sp.dk.dtype))
-            sp.dv.copy_(dv[:, off:off + n].to(sp.dv.dtype))
+            if sp.dk is not None:
+                sp.dk.copy_(dk[:, off:off + n].to(sp.dk.dtype))
+                sp.dv.copy_(dv[:, off:off + n].to(sp.dv.dtype))
             off += n
     if flags & 2:
-        dq.copy_(workspace.to(dq.dtype))
+        dq.copy_(dq_sum.to(dq.dtype))
     return workspace
 
 

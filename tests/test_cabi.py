@@ -59,8 +59,8 @@ def test_argument_rejection_without_a_gpu():
     p.g.dtype, p.g.head_dim = 0, 64
     assert lib.rswa_fwd(ctypes.byref(p), None) == -2          # unsupported head_dim
     assert b"head_dim" in lib.rswa_last_error()
-    # fp32 dQ accumulator + the delta rows + the scaled-lse rows
-    assert lib.rswa_bwd_workspace_bytes(1, 128, 2, 128) == 128 * 2 * 128 * 4 + 2 * (2 * 128 * 4)
+    # two fp32 rows (delta, scaled lse) per batch row and head, padded to whole 128-query tiles
+    assert lib.rswa_bwd_workspace_bytes(1, 130, 2, 128) == 2 * (2 * 256 * 4)
     assert lib.rswa_bwd_workspace_bytes(1, 128, 2, 64) == -1
     with pytest.raises(ValueError):
         _C.check(-1, "x")

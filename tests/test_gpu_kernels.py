@@ -165,7 +165,7 @@ def test_spans_emulated_ranks(cp, S, W, n_sink, lens):
 
 
 def test_two_phase_forward_and_split_backward():
-    """Query-tile ranges, the (local | halo) partials + merge path and INIT/FINISH-split backward."""
+    """Query-tile ranges, the (local | halo) partials + merge path and a backward split over two calls."""
     from ring_swa import _C
     K = _K()
     dev = torch.device("cuda")
@@ -201,7 +201,8 @@ def test_two_phase_forward_and_split_backward():
     halo.dk, halo.dv = torch.empty_like(kh), torch.empty_like(vh)
     local.dk, local.dv = torch.empty_like(kl), torch.empty_like(vl)
     ws = K.bwd(q, [halo], out, lse, do, dq, W, 0, scale, 300, flags=_C.BWD_INIT)
-    K.bwd(q, [local], out, lse, do, dq, W, 0, scale, 300, workspace=ws, flags=_C.BWD_FINISH)
+    seen = K.KVSpan(kh, vh, 0)      # second call: no gradient buffers for the halo, dq over both spans
+    K.bwd(q, [seen, local], out, lse, do, dq, W, 0, scale, 300, workspace=ws, flags=_C.BWD_FINISH)
     K.check_device_status()
     assert_close("dq", dq, qf.grad)
     assert_close("dk", torch.cat([halo.dk, local.dk], 1), kf.grad)
