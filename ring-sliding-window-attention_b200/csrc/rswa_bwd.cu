@@ -155,13 +155,13 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         const int h = hk * group + it / n_qt;
         const int row0 = (qt_first + it % n_qt) * kTile;
         const long long roff = b * p.d_sb + h * p.d_sh + row0;
-        if (it >= kQStages) ok = mbar_wait(&ctl->q_free[sq], ((it / kQStages) - 1) & 1, err, kErrWaitProducer);
+        if (it >= kQStages) ok = mbar_wait<200>(&ctl->q_free[sq], ((it / kQStages) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
         mbar_expect_tx(&ctl->q_full[sq], kStageTxBytes);
         tma_load_4d(sQ + sq * kTileBytes, &p.q_map, &ctl->q_full[sq], 0, h, row0, b);
         tma_load_4d(sQ + sq * kTileBytes + kBoxBytes, &p.q_map, &ctl->q_full[sq], 64, h, row0, b);
         bulk_load_1d(sLse + sq * kTile, p.lse2 + roff, kRowBytes, &ctl->q_full[sq]);
-        if (it >= 2) ok = mbar_wait(&ctl->do_free[sd], ((it >> 1) - 1) & 1, err, kErrWaitProducer);
+        if (it >= 2) ok = mbar_wait<200>(&ctl->do_free[sd], ((it >> 1) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
         mbar_expect_tx(&ctl->do_full[sd], kStageTxBytes);
         tma_load_4d(sDO + sd * kTileBytes, &p.do_map, &ctl->do_full[sd], 0, h, row0, b);
@@ -176,8 +176,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t dQk = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t dDOm = smem_desc_sw128(smem_u32(sDO), kBoxBytes, 1024);
-      bool ok = mbar_wait(&ctl->kv_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait(&ctl->q_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait<40>(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait<40>(&ctl->q_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -191,8 +191,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         if (it + 1 < n_iter) {
           // S^T of the next query tile, once every compute warp holds the current one in registers
           const int sq = (it + 1) % kQStages;
-          ok = mbar_wait(&ctl->q_full[sq], ((it + 1) / kQStages) & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait(&ctl->s_loaded, it & 1, err, kErrWaitMma);
+          ok = mbar_wait<40>(&ctl->q_full[sq], ((it + 1) / kQStages) & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait<40>(&ctl->s_loaded, it & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dQs = dQk + sq * kTile16;
@@ -203,7 +203,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
           }
           mma_commit(&ctl->s_ready);
         }
-        ok = mbar_wait(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+        ok = mbar_wait<40>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dDOs = dDOm + (it & 1) * kTile16;
@@ -223,8 +223,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       const uint64_t dV = smem_desc_sw128(smem_u32(sV), 16, 1024);
       const uint64_t dDOk = smem_desc_sw128(smem_u32(sDO), 16, 1024);
       const uint64_t dQm = smem_desc_sw128(smem_u32(sQ), kBoxBytes, 1024);
-      bool ok = mbar_wait(&ctl->kv_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait(&ctl->do_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait<40>(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait<40>(&ctl->do_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -235,7 +235,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         mma_commit(&ctl->dp_ready);
       }
       for (int it = 0; it < n_iter && ok; ++it) {
-        ok = mbar_wait(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+        ok = mbar_wait<40>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dQs = dQm + (it % kQStages) * kTile16;
@@ -247,8 +247,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         if (it + 1 < n_iter) {
           // dP^T of the next tile overwrites P^T | dS^T: behind dK (this thread) and dV (the other)
           const int sd = (it + 1) & 1;
-          ok = mbar_wait(&ctl->do_full[sd], ((it + 1) >> 1) & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait(&ctl->dv_done, it & 1, err, kErrWaitMma);
+          ok = mbar_wait<40>(&ctl->do_full[sd], ((it + 1) >> 1) & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait<40>(&ctl->dv_done, it & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dDOs = dDOk + sd * kTile16;

@@ -95,5 +95,6 @@ void set_error(const char* fmt, ...);
 int make_tile_map(CUtensorMap* map, const void* base, int dtype, int batch, int tokens, int heads,
                   long long sb, long long st, long long sh);
 int check_geom(const rswa_geom_t& g, bool need_grads);
+int sm_count();  // SMs of the current device (cached per device)
 
 }  // namespace rswa

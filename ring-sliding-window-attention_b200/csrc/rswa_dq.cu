@@ -119,12 +119,12 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int sk = j % kDqKStages, sv = j & 1;
-        if (j >= kDqKStages) ok = mbar_wait(&ctl->k_free[sk], ((j / kDqKStages) - 1) & 1, err, kErrWaitProducer);
+        if (j >= kDqKStages) ok = mbar_wait<200>(&ctl->k_free[sk], ((j / kDqKStages) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
         mbar_expect_tx(&ctl->k_full[sk], kTileBytes);
         tma_load_4d(sK + sk * kTileBytes, &p.k_map[c.span], &ctl->k_full[sk], 0, hk, c.tok, b);
         tma_load_4d(sK + sk * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[sk], 64, hk, c.tok, b);
-        if (j >= 2) ok = mbar_wait(&ctl->v_free[sv], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
+        if (j >= 2) ok = mbar_wait<200>(&ctl->v_free[sv], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
         mbar_expect_tx(&ctl->v_full[sv], kTileBytes);
         tma_load_4d(sV + sv * kTileBytes, &p.v_map[c.span], &ctl->v_full[sv], 0, hk, c.tok, b);
@@ -139,8 +139,8 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
       const uint64_t dQd = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t dKk = smem_desc_sw128(smem_u32(sK), 16, 1024);        // K as K-major B of S
       const uint64_t dKm = smem_desc_sw128(smem_u32(sK), kBoxBytes, 1024); // K as MN-major B of dQ
-      bool ok = mbar_wait(&ctl->q_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait(&ctl->k_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait<40>(&ctl->q_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait<40>(&ctl->k_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -156,7 +156,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
           // S of the next tile into the other buffer; its previous content (dS of tile j-1) was
           // consumed by a product this thread issued earlier
           const int sk = (j + 1) % kDqKStages;
-          ok = mbar_wait(&ctl->k_full[sk], ((j + 1) / kDqKStages) & 1, err, kErrWaitMma);
+          ok = mbar_wait<40>(&ctl->k_full[sk], ((j + 1) / kDqKStages) & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dKs = dKk + sk * kTile16;
@@ -167,7 +167,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
           }
           mma_commit(&ctl->s_ready[(j + 1) & 1]);
         }
-        ok = mbar_wait(&ctl->ds_ready, j & 1, err, kErrWaitMma);
+        ok = mbar_wait<40>(&ctl->ds_ready, j & 1, err, kErrWaitMma);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dKj = dKm + (j % kDqKStages) * kTile16;
@@ -184,12 +184,12 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
       constexpr uint32_t kTile16 = kTileBytes >> 4;
       const uint64_t dDO = smem_desc_sw128(smem_u32(sDO), 16, 1024);
       const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      bool ok = mbar_wait(&ctl->q_full, 0, err, kErrWaitMma);
+      bool ok = mbar_wait<40>(&ctl->q_full, 0, err, kErrWaitMma);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int sv = j & 1;
-        ok = mbar_wait(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
+        ok = mbar_wait<40>(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
         // the compute warps must have read dP of the previous tile out of TMEM
-        if (ok && j > 0) ok = mbar_wait(&ctl->dp_loaded, (j - 1) & 1, err, kErrWaitMma);
+        if (ok && j > 0) ok = mbar_wait<40>(&ctl->dp_loaded, (j - 1) & 1, err, kErrWaitMma);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dVs = dVk + sv * kTile16;

@@ -123,12 +123,12 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1, sk = j % kKStages;
-        if (j >= kKStages) ok = mbar_wait(&ctl->k_free[sk], ((j / kKStages) - 1) & 1, err, kErrWaitProducer);
+        if (j >= kKStages) ok = mbar_wait<200>(&ctl->k_free[sk], ((j / kKStages) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
         mbar_expect_tx(&ctl->k_full[sk], kTileBytes);
         tma_load_4d(sK + sk * kTileBytes, &p.k_map[c.span], &ctl->k_full[sk], 0, hk, c.tok, b);
         tma_load_4d(sK + sk * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[sk], 64, hk, c.tok, b);
-        if (j >= 2) ok = mbar_wait(&ctl->v_free[st], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
+        if (j >= 2) ok = mbar_wait<200>(&ctl->v_free[st], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
         mbar_expect_tx(&ctl->v_full[st], kTileBytes);
         tma_load_4d(sV + st * kTileBytes, &p.v_map[c.span], &ctl->v_full[st], 0, hk, c.tok, b);
@@ -151,8 +151,8 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       int n_pv = 0;  // products O_w += P_w V issued so far (also the phase of p_ready[w])
       TileCursor cur, nxt;
       cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
-      bool ok = mbar_wait(&ctl->q_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait(&ctl->k_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait<40>(&ctl->q_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait<40>(&ctl->k_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
         if (tile_active(geom, w, cur, p.n_sink)) {
@@ -170,11 +170,11 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
         const int sv = j & 1, sk = (j + 1) % kKStages;
         nxt = cur;
         cursor_next<kTile>(geom, p.span_pos, p.span_len, nxt, more);
-        ok = mbar_wait(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
-        if (ok && more) ok = mbar_wait(&ctl->k_full[sk], ((j + 1) / kKStages) & 1, err, kErrWaitMma);
+        ok = mbar_wait<40>(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
+        if (ok && more) ok = mbar_wait<40>(&ctl->k_full[sk], ((j + 1) / kKStages) & 1, err, kErrWaitMma);
         if (!ok) break;
         if (tile_active(geom, w, cur, p.n_sink)) {
-          ok = mbar_wait(&ctl->p_ready[w], n_pv & 1, err, kErrWaitMma);
+          ok = mbar_wait<40>(&ctl->p_ready[w], n_pv & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dVs = dV + sv * kTile16;

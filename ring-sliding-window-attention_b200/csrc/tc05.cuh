@@ -57,6 +57,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises *err_flag) when the limit is hit or when another
 // thread of the CTA has already raised the flag, so that every role unwinds together.
+// kSleepNs > 0 backs off between polls: a waiting producer or MMA-issuing thread must not steal
+// issue slots from the compute warps that share its scheduler.
+template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* err_flag,
                                           int code) {
   // Two limits: a poll count and wall time (try_wait may itself suspend the thread for a while, so
@@ -64,6 +67,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint64_t t_start = 0;
   for (uint32_t i = 0; i < RSWA_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (kSleepNs > 0) __nanosleep(kSleepNs);
     if ((i & 255u) == 255u) {
       if (*err_flag != 0) return false;
       uint64_t now;
@@ -94,6 +98,14 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0),
         "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+
+// Pulls a tile into L2 ahead of its load into shared memory (no completion tracking needed).
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* m, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
 }
 
 // 1-D bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes).
