@@ -10,7 +10,8 @@ sequence is sharded over the ranks: by default each rank keeps the 1-GPU chunk (
 
 One JSON line is printed by rank 0.  `value` is timed with inputs resident in HBM; `e2e` adds the
 host->device copy of q, k, v, dO from pinned memory and the device->host copy of out, dq, dk, dv every
-step; `roofline` is the backward kernel (the dominant one) timed with CUDA events on its stream;
+step; `roofline` is the dK/dV backward kernel (the longest one) timed with CUDA events on its stream, `roofline_dq`
+and `roofline_fwd` the other two tensor-core kernels;
 `cpu_baseline` is the dense torch CPU restatement of the reference's test oracle on a bounded slice.
 
 `--impl reference` times that CPU restatement alone (the reference's own attention arithmetic lives in
@@ -46,6 +47,9 @@ WORKLOADS = {
     # reduced case for profiler captures: same kernels, inputs still larger than L2, < 1 GB on the device
     "small": dict(fn="ring_sliding_window_attn", B=1, S=16384, Hq=16, Hkv=16, W=1000, n_sink=0, seed=1),
 }
+# DRAM bytes (read + write) of one dK/dV-kernel launch on cfg2, from an ncu capture of the "small"
+# workload scaled by the number of key tiles (see profiles/); None until measured
+TRAFFIC_DKDV_CFG2 = 3.02e9
 # cpu sample: a slice of the workload small enough for dense S x S attention on host cores
 CPU_SAMPLE = dict(S=4096, H=2)
 
@@ -277,9 +281,11 @@ def main():
     launches = K.launch_count - launches0
     lib = _C.lib()
     fwd_ms = sum(lib.rswa_event_elapsed_ms(a, b) for a, b in K.fwd_events) / args.steps
-    bwd_ms = sum(lib.rswa_event_elapsed_ms(a, b) for a, b in K.bwd_main_events) / args.steps
-    for a, b in K.fwd_events + K.bwd_main_events:
-        lib.rswa_event_destroy(a), lib.rswa_event_destroy(b)
+    bwd_ms = sum(lib.rswa_event_elapsed_ms(a, m) for a, m, b in K.bwd_main_events) / args.steps     # dK/dV kernel
+    dq_ms = sum(lib.rswa_event_elapsed_ms(m, b) for a, m, b in K.bwd_main_events) / args.steps      # dQ kernel
+    for evs in K.fwd_events + K.bwd_main_events:
+        for e in evs:
+            lib.rswa_event_destroy(e)
     K.fwd_events = K.bwd_main_events = None
     K.check_device_status(dev)
 
@@ -313,10 +319,11 @@ def main():
     clocks = sampler.stop() if sampler else None
 
     # ---------------------------------------------------------------- reduce over ranks
-    stats = torch.tensor([ms, fwd_ms, bwd_ms, e2e_ms if not args.no_e2e else 0.0], device=dev, dtype=torch.float64)
+    stats = torch.tensor([ms, fwd_ms, bwd_ms, e2e_ms if not args.no_e2e else 0.0, dq_ms], device=dev,
+                         dtype=torch.float64)
     if n > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    ms, fwd_ms, bwd_ms, e2e_ms = stats.tolist()
+    ms, fwd_ms, bwd_ms, e2e_ms, dq_ms = stats.tolist()
 
     if rank == 0:
         tokens = B * S_g
@@ -329,9 +336,13 @@ def main():
             pairs_total = B * visible_pairs(0, S_g, W, n_sink)
         # work is near-uniform over ranks except the first ones; the slowest rank is the last
         pairs_rank = B * visible_pairs(S_g - S, S_g, W, n_sink) if not varlen else pairs_total / n
-        flops_bwd = 10 * D * Hq * pairs_rank
+        # algorithmic FLOPs on visible pairs: dK/dV kernel 4 products (S^T, dP^T, dV, dK), dQ kernel 3 (S, dP,
+        # dQ; the recomputed S and dP are counted because the kernel executes them), forward 2
+        flops_bwd = 8 * D * Hq * pairs_rank
+        flops_dq = 6 * D * Hq * pairs_rank
         flops_fwd = 4 * D * Hq * pairs_rank
         ach_bwd = flops_bwd / (bwd_ms * 1e-3) / 1e12
+        ach_dq = flops_dq / (dq_ms * 1e-3) / 1e12
         ach_fwd = flops_fwd / (fwd_ms * 1e-3) / 1e12
         line = {
             "metric": "ring SWA fwd+bwd tokens/s", "value": tokens / (ms_step * 1e-3), "unit": "tokens/s",
@@ -340,10 +351,13 @@ def main():
             "data": "synthetic", "config": workload_config(args, wl, n),
             "tflops_per_gpu_in_window": 14 * D * Hq * pairs_total / n / (ms_step * 1e-3) / 1e12,
             "frac_of_bf16_peak": 14 * D * Hq * pairs_total / n / (ms_step * 1e-3) / 1e12 / peak_tf,
-            "roofline": {"kernel": "rswa_bwd_kernel", "bound": "tensor", "achieved": ach_bwd, "peak": peak_tf,
-                         "unit": "TFLOP/s", "frac": ach_bwd / peak_tf, "traffic": None,
+            "roofline": {"kernel": "rswa_bwd_kernel (dK/dV)", "bound": "tensor", "achieved": ach_bwd, "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": ach_bwd / peak_tf, "traffic": TRAFFIC_DKDV_CFG2 if args.workload == "cfg2" and n == 1 else None,
                          "peak_source": f"{peak_kind} bf16_tflops (burst)", "ms_per_launch": bwd_ms,
                          "algorithmic_flops_per_launch": flops_bwd},
+            "roofline_dq": {"kernel": "rswa_dq_kernel", "bound": "tensor", "achieved": ach_dq, "peak": peak_tf,
+                            "unit": "TFLOP/s", "frac": ach_dq / peak_tf, "ms_per_launch": dq_ms,
+                            "algorithmic_flops_per_launch": flops_dq},
             "roofline_fwd": {"kernel": "rswa_fwd_kernel", "bound": "tensor", "achieved": ach_fwd, "peak": peak_tf,
                              "unit": "TFLOP/s", "frac": ach_fwd / peak_tf, "ms_per_launch": fwd_ms},
             "gpu_launches": launches,

@@ -126,6 +126,7 @@ typedef struct rswa_bwd_params {
    * NULL to skip. */
   void* ev_main_start;
   void* ev_main_stop;
+  void* ev_main_mid; /* optional: recorded between the dK/dV kernel and the dQ kernel */
 } rswa_bwd_params_t;
 
 int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_t n_q_heads, int32_t head_dim);

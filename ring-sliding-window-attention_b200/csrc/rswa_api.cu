@@ -336,6 +336,7 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
     rc = launch_bwd(kk, g.dtype, total_tiles, stream);
     if (rc) return rc;
   }
+  if (p->ev_main_mid) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_mid), stream);
   if (want_dq) {
     rc = launch_dq(kq, g.dtype, stream);
     if (rc) return rc;

@@ -59,7 +59,7 @@ class BwdParams(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("flags", C.c_int32),
         ("status", C.c_void_p),
-        ("ev_main_start", C.c_void_p), ("ev_main_stop", C.c_void_p),
+        ("ev_main_start", C.c_void_p), ("ev_main_stop", C.c_void_p), ("ev_main_mid", C.c_void_p),
     ]
 
 

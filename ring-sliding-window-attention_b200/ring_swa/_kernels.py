@@ -35,8 +35,9 @@ _status = {}
 # Number of kernels of this library launched so far (benchmarks report the count per timed region).
 launch_count = 0
 
-# When set to a list, every main backward kernel is bracketed by a fresh pair of timing events which
-# is appended here as (start, stop) raw handles; benchmarks read them with rswa_event_elapsed_ms.
+# When set to a list, every rswa_bwd call records three fresh timing events, appended here as raw handles
+# (start, mid, stop): start..mid brackets the dK/dV kernel, mid..stop the dQ kernel; benchmarks read them
+# with rswa_event_elapsed_ms.
 bwd_main_events = None
 # Same for the forward kernel (one launch per rswa_fwd call).
 fwd_events = None
@@ -205,8 +206,8 @@ def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.
     p.flags = int(flags)
     p.status = status_word(q.device).data_ptr()
     if bwd_main_events is not None:
-        p.ev_main_start, p.ev_main_stop = _C.lib().rswa_event_create(), _C.lib().rswa_event_create()
-        bwd_main_events.append((p.ev_main_start, p.ev_main_stop))
+        p.ev_main_start, p.ev_main_mid, p.ev_main_stop = (_C.lib().rswa_event_create() for _ in range(3))
+        bwd_main_events.append((p.ev_main_start, p.ev_main_mid, p.ev_main_stop))
     _C.check(_C.lib().rswa_bwd(C.byref(p), _stream()), "rswa_bwd")
     global launch_count
     launch_count += ((1 if flags & _C.BWD_INIT else 0) + (1 if any(s.dk is not None for s in spans) else 0) +
