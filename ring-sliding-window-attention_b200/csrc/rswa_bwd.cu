@@ -30,6 +30,7 @@ using namespace tc05;
 namespace {
 
 constexpr int kBwdThreads = 384;  // warp 0 TMA, warps 1-2 MMA, warp 3 idle, warps 4-11 compute
+constexpr int kMmaPollNs = 0;  // the MMA-issuing threads poll without back-off (they are on the critical path)
 constexpr int kBwdTmemCols = 512;
 constexpr int kComputeThreads = 256;
 constexpr int kQStages = 3;
@@ -176,8 +177,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t dQk = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t dDOm = smem_desc_sw128(smem_u32(sDO), kBoxBytes, 1024);
-      bool ok = mbar_wait<40>(&ctl->kv_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait<40>(&ctl->q_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->q_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -191,8 +192,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         if (it + 1 < n_iter) {
           // S^T of the next query tile, once every compute warp holds the current one in registers
           const int sq = (it + 1) % kQStages;
-          ok = mbar_wait<40>(&ctl->q_full[sq], ((it + 1) / kQStages) & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait<40>(&ctl->s_loaded, it & 1, err, kErrWaitMma);
+          ok = mbar_wait<kMmaPollNs>(&ctl->q_full[sq], ((it + 1) / kQStages) & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->s_loaded, it & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dQs = dQk + sq * kTile16;
@@ -203,7 +204,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
           }
           mma_commit(&ctl->s_ready);
         }
-        ok = mbar_wait<40>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+        ok = mbar_wait<kMmaPollNs>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dDOs = dDOm + (it & 1) * kTile16;
@@ -223,8 +224,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       const uint64_t dV = smem_desc_sw128(smem_u32(sV), 16, 1024);
       const uint64_t dDOk = smem_desc_sw128(smem_u32(sDO), 16, 1024);
       const uint64_t dQm = smem_desc_sw128(smem_u32(sQ), kBoxBytes, 1024);
-      bool ok = mbar_wait<40>(&ctl->kv_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait<40>(&ctl->do_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->do_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -235,7 +236,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         mma_commit(&ctl->dp_ready);
       }
       for (int it = 0; it < n_iter && ok; ++it) {
-        ok = mbar_wait<40>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+        ok = mbar_wait<kMmaPollNs>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dQs = dQm + (it % kQStages) * kTile16;
@@ -247,8 +248,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         if (it + 1 < n_iter) {
           // dP^T of the next tile overwrites P^T | dS^T: behind dK (this thread) and dV (the other)
           const int sd = (it + 1) & 1;
-          ok = mbar_wait<40>(&ctl->do_full[sd], ((it + 1) >> 1) & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait<40>(&ctl->dv_done, it & 1, err, kErrWaitMma);
+          ok = mbar_wait<kMmaPollNs>(&ctl->do_full[sd], ((it + 1) >> 1) & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->dv_done, it & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dDOs = dDOk + sd * kTile16;

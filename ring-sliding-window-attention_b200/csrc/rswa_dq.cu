@@ -1,21 +1,27 @@
 // dQ kernel: the query-stationary half of the backward pass.
 //
-// One CTA owns one 128-row query tile of one head and walks the key tiles its rows can see, over
-// every KV span of the call (sink | halo | local), so that dQ is accumulated on chip and written
-// exactly once -- no atomics, no fp32 accumulator in global memory:
+// A work item is one 128-row query tile of one head; the CTA walks the key tiles the item's rows can
+// see, over every KV span of the call (sink | halo | local), so that dQ is accumulated on chip and
+// written exactly once -- no atomics, no fp32 accumulator in global memory:
 //
 //   S  = Q K^T          A = Q  (smem, K-major)   B = K (smem, K-major)     two TMEM buffers
 //   dP = dO V^T         A = dO (smem, K-major)   B = V (smem, K-major)
-//   P  = exp2(S * scale_log2 - lse2[row]),  dS = P * (dP - delta[row])      (8 compute warps)
+//   P  = exp2(S * scale_log2 - lse2[row]),  dS = P * (dP - delta[row])      (16 compute warps)
 //   dQ += dS K          A = dS (TMEM, written over S)   B = K (smem, MN-major)
 //
 // P is recomputed from the final log-sum-exp, so the result is exact for any set of spans
 // (the property the reference's per-hop backward relies on, ring_swa/ops/attn.py:63-126).
-// S of the next key tile is produced while the compute warps still work on the current one (two S
-// buffers), dP of the next tile as soon as the current dP has been read.  Two warps issue MMAs
-// (S and dQ from one, dP from the other) because the issue path, not the tensor pipe, is what a
-// single thread saturates first.
-// TMEM: [0,128) S_0/dS_0, [128,256) S_1/dS_1, [256,384) dP, [384,512) dQ.
+//
+// The kernel is persistent: one CTA per SM takes items blockIdx.x, blockIdx.x + gridDim.x, ... and
+// every pipeline (K/V rings, S buffers, barrier phases) keeps running across item boundaries, so
+// the fill and drain of one item (first loads, last dQ product, dQ write-out) overlap the next
+// item's loads and products instead of leaving the SM idle.  Roles:
+//   warp 0      TMA producer (Q, dO once per item; K ring of 3, V ring of 2)
+//   warp 1      issues S and dQ products       warp 2   issues dP products
+//   warp 3      computes the key-tile list of the coming item into a two-slot ring
+//   warps 4-19  compute, four warps per TMEM lane quadrant, 32 key columns each
+// Two warps issue MMAs because the issue path, not the tensor pipe, is what one thread saturates
+// first.  TMEM: [0,128) S_0/dS_0, [128,256) S_1/dS_1, [256,384) dP, [384,512) dQ.
 #include "rswa_common.cuh"
 #include "rswa_tiles.cuh"
 #include "tc05.cuh"
@@ -25,36 +31,56 @@ using namespace tc05;
 
 namespace {
 
-constexpr int kDqThreads = 384;  // warp 0 TMA, warps 1-2 MMA, warp 3 idle, warps 4-11 compute
+constexpr int kDqThreads = 640;
 constexpr int kDqTmemCols = 512;
 constexpr int kDqKStages = 3;
 constexpr int kDqSmemTiles = 7 * kTileBytes;  // Q, dO, K x 3, V x 2
-constexpr int kDqCompute = 256;
+constexpr int kDqCompute = 512;
+// The MMA-issuing threads poll their barriers without back-off: they sit on the critical path of
+// every key tile, and a sleeping poll was measured slower.
+constexpr int kMmaPollNs = 0;
+constexpr int kDqGeomUsers = 3 + kDqCompute / 32;  // producer, two MMA issuers, one lane per compute warp
 
 struct DqCtl {
-  uint64_t q_full, k_full[kDqKStages], v_full[2], k_free[kDqKStages], v_free[2];
-  uint64_t s_ready[2], dp_ready, dp_loaded, ds_ready, done;
+  uint64_t q_full, do_full, q_free, do_free;
+  uint64_t k_full[kDqKStages], v_full[2], k_free[kDqKStages], v_free[2];
+  uint64_t s_ready[2], dp_ready, dp_loaded, ds_ready, done, dq_drained;
+  uint64_t geom_full[2], geom_free[2];
   uint32_t tmem_base;
   int err;
-  QBlockGeom geom;
+  QBlockGeom geom[2];
 };
 
 constexpr int kDqSmemBytes = kDqSmemTiles + 1024;
 static_assert(sizeof(DqCtl) <= 1024, "control block too large");
 static_assert(kDqSmemBytes <= 232448, "shared memory budget");
 
-__device__ __forceinline__ void bar_sync_pair(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+// the four compute warps that share a TMEM lane quadrant
+__device__ __forceinline__ void bar_sync_quad(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+
+struct DqItem {
+  int qt, h, b, hk, row0;
+};
+__device__ __forceinline__ DqItem dq_item(const BwdKernelParams& p, int n_q_tiles, int it) {
+  DqItem d;  // query tile fastest, then head, then batch row
+  d.qt = it % n_q_tiles;
+  it /= n_q_tiles;
+  d.h = it % p.hq;
+  d.b = it / p.hq;
+  d.hk = d.h / (p.hq / p.hkv);
+  d.row0 = d.qt * kTile;
+  return d;
+}
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kDqThreads, 1)
-rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
+rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_items) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sDO = smem + kTileBytes;
   uint8_t* sK = smem + 2 * kTileBytes;  // three stages
   uint8_t* sV = smem + 5 * kTileBytes;  // two stages
   DqCtl* ctl = reinterpret_cast<DqCtl*>(smem + kDqSmemTiles);
-  QBlockGeom* geom = &ctl->geom;
 
   // a device-side error was already reported on this stream: do not pile further time-outs on it
   if (__syncthreads_or(*reinterpret_cast<volatile int*>(p.status) != 0)) return;
@@ -62,17 +88,11 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // work item: query tile fastest, then head, then batch row
-  int idx = blockIdx.x;
-  const int qt = idx % n_q_tiles;
-  idx /= n_q_tiles;
-  const int h = idx % p.hq;
-  const int b = idx / p.hq;
-  const int hk = h / (p.hq / p.hkv);
-  const int row0 = qt * kTile;
-
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
+    mbar_init(&ctl->do_full, 1);
+    mbar_init(&ctl->q_free, 1);
+    mbar_init(&ctl->do_free, 1);
     for (int i = 0; i < kDqKStages; ++i) {
       mbar_init(&ctl->k_full[i], 1);
       mbar_init(&ctl->k_free[i], 1);
@@ -81,16 +101,16 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
       mbar_init(&ctl->v_full[i], 1);
       mbar_init(&ctl->v_free[i], 1);
       mbar_init(&ctl->s_ready[i], 1);
+      mbar_init(&ctl->geom_full[i], 1);
+      mbar_init(&ctl->geom_free[i], kDqGeomUsers);
     }
     mbar_init(&ctl->dp_ready, 1);
     mbar_init(&ctl->dp_loaded, kDqCompute);
     mbar_init(&ctl->ds_ready, kDqCompute);
     mbar_init(&ctl->done, 1);
+    mbar_init(&ctl->dq_drained, kDqCompute);
     ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
     mbar_fence_init();
-    // a block of one query tile: the second tile of the geometry stays empty
-    qblock_geometry<kTile>(geom, p.cu, p.n_seqs, p.n_spans, p.span_pos, p.span_len, p.q_pos_start, p.q_len,
-                           p.window, p.n_sink, qt, qt + 1);
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, kDqTmemCols);
@@ -103,35 +123,73 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
   const uint32_t tmem = ctl->tmem_base;
   const uint32_t tDP = tmem + 256, tDQ = tmem + 384;
   volatile int* err = &ctl->err;
-  const int n_tiles = (ctl->err != 0) ? 0 : geom->n_tiles;
+  const int it0 = (ctl->err != 0) ? n_items : static_cast<int>(blockIdx.x);
+  const int it_step = static_cast<int>(gridDim.x);
 
   if (warp < 4) {
-    setmaxnreg_dec<64>();
-    if (warp == 0 && lane == 0 && n_tiles > 0) {
-      // ------------------------------------------------------------------ TMA producer
-      mbar_expect_tx(&ctl->q_full, 2 * kTileBytes);
-      tma_load_4d(sQ, &p.q_map, &ctl->q_full, 0, h, row0, b);
-      tma_load_4d(sQ + kBoxBytes, &p.q_map, &ctl->q_full, 64, h, row0, b);
-      tma_load_4d(sDO, &p.do_map, &ctl->q_full, 0, h, row0, b);
-      tma_load_4d(sDO + kBoxBytes, &p.do_map, &ctl->q_full, 64, h, row0, b);
-      TileCursor c;
-      cursor_begin<kTile>(geom, p.span_pos, p.span_len, c);
+    setmaxnreg_dec<56>();
+    if (warp == 3 && lane == 0) {
+      // ------------------------------------------------------------------ key-tile lists, one item ahead
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int sk = j % kDqKStages, sv = j & 1;
-        if (j >= kDqKStages) ok = mbar_wait<200>(&ctl->k_free[sk], ((j / kDqKStages) - 1) & 1, err, kErrWaitProducer);
+      int n = 0;
+      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+        const int slot = n & 1;
+        if (n >= 2) ok = mbar_wait<200>(&ctl->geom_free[slot], ((n >> 1) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
-        mbar_expect_tx(&ctl->k_full[sk], kTileBytes);
-        tma_load_4d(sK + sk * kTileBytes, &p.k_map[c.span], &ctl->k_full[sk], 0, hk, c.tok, b);
-        tma_load_4d(sK + sk * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[sk], 64, hk, c.tok, b);
-        if (j >= 2) ok = mbar_wait<200>(&ctl->v_free[sv], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
-        if (!ok) break;
-        mbar_expect_tx(&ctl->v_full[sv], kTileBytes);
-        tma_load_4d(sV + sv * kTileBytes, &p.v_map[c.span], &ctl->v_full[sv], 0, hk, c.tok, b);
-        tma_load_4d(sV + sv * kTileBytes + kBoxBytes, &p.v_map[c.span], &ctl->v_full[sv], 64, hk, c.tok, b);
-        cursor_next<kTile>(geom, p.span_pos, p.span_len, c, j + 1 < n_tiles);
+        const int qt = it % n_q_tiles;
+        // a block of one query tile: the second tile of the geometry stays empty
+        qblock_geometry<kTile>(&ctl->geom[slot], p.cu, p.n_seqs, p.n_spans, p.span_pos, p.span_len, p.q_pos_start,
+                               p.q_len, p.window, p.n_sink, qt, qt + 1);
+        mbar_arrive(&ctl->geom_full[slot]);
       }
-    } else if (warp == 1 && lane == 0 && n_tiles > 0) {
+    } else if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      bool ok = true;
+      int n = 0, kc = 0, ic = 0;  // items seen, K/V tiles loaded so far, items with work so far
+      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+        const int slot = n & 1;
+        ok = mbar_wait<200>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitProducer);
+        if (!ok) break;
+        const QBlockGeom* geom = &ctl->geom[slot];
+        const int n_tiles = geom->n_tiles;
+        if (n_tiles > 0) {
+          const DqItem w = dq_item(p, n_q_tiles, it);
+          // Q may be replaced once the last S product of the previous item has read it
+          if (ic > 0) ok = mbar_wait<200>(&ctl->q_free, (ic - 1) & 1, err, kErrWaitProducer);
+          if (!ok) break;
+          mbar_expect_tx(&ctl->q_full, kTileBytes);
+          tma_load_4d(sQ, &p.q_map, &ctl->q_full, 0, w.h, w.row0, w.b);
+          tma_load_4d(sQ + kBoxBytes, &p.q_map, &ctl->q_full, 64, w.h, w.row0, w.b);
+          TileCursor c;
+          cursor_begin<kTile>(geom, p.span_pos, p.span_len, c);
+          for (int j = 0; j < n_tiles && ok; ++j, ++kc) {
+            const int sk = kc % kDqKStages, sv = kc & 1;
+            if (kc >= kDqKStages)
+              ok = mbar_wait<200>(&ctl->k_free[sk], ((kc / kDqKStages) - 1) & 1, err, kErrWaitProducer);
+            if (!ok) break;
+            mbar_expect_tx(&ctl->k_full[sk], kTileBytes);
+            tma_load_4d(sK + sk * kTileBytes, &p.k_map[c.span], &ctl->k_full[sk], 0, w.hk, c.tok, w.b);
+            tma_load_4d(sK + sk * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[sk], 64, w.hk, c.tok, w.b);
+            if (j == 0) {
+              // dO likewise, after the last dP product of the previous item
+              if (ic > 0) ok = mbar_wait<200>(&ctl->do_free, (ic - 1) & 1, err, kErrWaitProducer);
+              if (!ok) break;
+              mbar_expect_tx(&ctl->do_full, kTileBytes);
+              tma_load_4d(sDO, &p.do_map, &ctl->do_full, 0, w.h, w.row0, w.b);
+              tma_load_4d(sDO + kBoxBytes, &p.do_map, &ctl->do_full, 64, w.h, w.row0, w.b);
+            }
+            if (kc >= 2) ok = mbar_wait<200>(&ctl->v_free[sv], ((kc >> 1) - 1) & 1, err, kErrWaitProducer);
+            if (!ok) break;
+            mbar_expect_tx(&ctl->v_full[sv], kTileBytes);
+            tma_load_4d(sV + sv * kTileBytes, &p.v_map[c.span], &ctl->v_full[sv], 0, w.hk, c.tok, w.b);
+            tma_load_4d(sV + sv * kTileBytes + kBoxBytes, &p.v_map[c.span], &ctl->v_full[sv], 64, w.hk, c.tok, w.b);
+            cursor_next<kTile>(geom, p.span_pos, p.span_len, c, j + 1 < n_tiles);
+          }
+          ++ic;
+        }
+        if (ok) mbar_arrive(&ctl->geom_free[slot]);
+      }
+    } else if (warp == 1 && lane == 0) {
       // ------------------------------------------------------------------ MMA issuer 1: S and dQ
       constexpr uint32_t id_kk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t id_tn = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
@@ -139,177 +197,219 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
       const uint64_t dQd = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t dKk = smem_desc_sw128(smem_u32(sK), 16, 1024);        // K as K-major B of S
       const uint64_t dKm = smem_desc_sw128(smem_u32(sK), kBoxBytes, 1024); // K as MN-major B of dQ
-      bool ok = mbar_wait<40>(&ctl->q_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait<40>(&ctl->k_full[0], 0, err, kErrWaitMma);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-          mma_ss(tmem, dQd + off, dKk + off, id_kk, k > 0 ? 1u : 0u);
-        }
-        mma_commit(&ctl->s_ready[0]);
-      }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const bool more = j + 1 < n_tiles;
-        if (more) {
-          // S of the next tile into the other buffer; its previous content (dS of tile j-1) was
-          // consumed by a product this thread issued earlier
-          const int sk = (j + 1) % kDqKStages;
-          ok = mbar_wait<40>(&ctl->k_full[sk], ((j + 1) / kDqKStages) & 1, err, kErrWaitMma);
+      bool ok = true;
+      int n = 0, kc = 0, ic = 0;  // kc: key tiles of earlier items, the running index of this item's tile 0
+      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+        const int slot = n & 1;
+        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
+        if (!ok) break;
+        const int n_tiles = ctl->geom[slot].n_tiles;
+        if (n_tiles > 0) {
+          // S of the item's first tile.  The S buffers keep alternating across items, so the buffer
+          // written here last held dS of a tile whose dQ product this thread issued earlier.
+          ok = mbar_wait<kMmaPollNs>(&ctl->q_full, ic & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->k_full[kc % kDqKStages], (kc / kDqKStages) & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t dKs = dKk + sk * kTile16;
+          {
+            const uint64_t dKs = dKk + (kc % kDqKStages) * kTile16;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-            mma_ss(tmem + 128 * ((j + 1) & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+              mma_ss(tmem + 128 * (kc & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
+            }
+            mma_commit(&ctl->s_ready[kc & 1]);
+            if (n_tiles == 1) mma_commit(&ctl->q_free);
           }
-          mma_commit(&ctl->s_ready[(j + 1) & 1]);
-        }
-        ok = mbar_wait<40>(&ctl->ds_ready, j & 1, err, kErrWaitMma);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t dKj = dKm + (j % kDqKStages) * kTile16;
+          for (int j = 0; j < n_tiles && ok; ++j) {
+            const int g = kc + j;
+            if (j + 1 < n_tiles) {
+              const int sk = (g + 1) % kDqKStages;
+              ok = mbar_wait<kMmaPollNs>(&ctl->k_full[sk], ((g + 1) / kDqKStages) & 1, err, kErrWaitMma);
+              if (!ok) break;
+              tc_fence_after();
+              const uint64_t dKs = dKk + sk * kTile16;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          mma_ts(tDQ, tmem + 128 * (j & 1) + k * 8, dKj + k * 128, id_tn, (j > 0 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < 8; ++k) {
+                const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+                mma_ss(tmem + 128 * ((g + 1) & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
+              }
+              mma_commit(&ctl->s_ready[(g + 1) & 1]);
+              if (j + 2 == n_tiles) mma_commit(&ctl->q_free);  // that was the item's last read of Q
+            }
+            ok = mbar_wait<kMmaPollNs>(&ctl->ds_ready, g & 1, err, kErrWaitMma);
+            // the first product of an item overwrites dQ: the previous item's must have been read out
+            if (ok && j == 0 && ic > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dq_drained, (ic - 1) & 1, err, kErrWaitMma);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t dKj = dKm + (g % kDqKStages) * kTile16;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              mma_ts(tDQ, tmem + 128 * (g & 1) + k * 8, dKj + k * 128, id_tn, (j > 0 || k > 0) ? 1u : 0u);
+            }
+            mma_commit(&ctl->k_free[g % kDqKStages]);
+          }
+          if (ok) mma_commit(&ctl->done);
+          kc += n_tiles;
+          ++ic;
         }
-        mma_commit(&ctl->k_free[j % kDqKStages]);
+        if (ok) mbar_arrive(&ctl->geom_free[slot]);
       }
-      if (ok) mma_commit(&ctl->done);
-    } else if (warp == 2 && lane == 0 && n_tiles > 0) {
+    } else if (warp == 2 && lane == 0) {
       // ------------------------------------------------------------------ MMA issuer 2: dP
       constexpr uint32_t id_kk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t kTile16 = kTileBytes >> 4;
       const uint64_t dDO = smem_desc_sw128(smem_u32(sDO), 16, 1024);
       const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      bool ok = mbar_wait<40>(&ctl->q_full, 0, err, kErrWaitMma);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int sv = j & 1;
-        ok = mbar_wait<40>(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
-        // the compute warps must have read dP of the previous tile out of TMEM
-        if (ok && j > 0) ok = mbar_wait<40>(&ctl->dp_loaded, (j - 1) & 1, err, kErrWaitMma);
+      bool ok = true;
+      int n = 0, kc = 0, ic = 0;
+      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+        const int slot = n & 1;
+        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
         if (!ok) break;
-        tc_fence_after();
-        const uint64_t dVs = dVk + sv * kTile16;
+        const int n_tiles = ctl->geom[slot].n_tiles;
+        if (n_tiles > 0) {
+          ok = mbar_wait<kMmaPollNs>(&ctl->do_full, ic & 1, err, kErrWaitMma);
+          for (int j = 0; j < n_tiles && ok; ++j) {
+            const int g = kc + j;
+            const int sv = g & 1;
+            ok = mbar_wait<kMmaPollNs>(&ctl->v_full[sv], (g >> 1) & 1, err, kErrWaitMma);
+            // the compute warps must have read dP of the previous tile out of TMEM
+            if (ok && g > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dp_loaded, (g - 1) & 1, err, kErrWaitMma);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t dVs = dVk + sv * kTile16;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-          mma_ss(tDP, dDO + off, dVs + off, id_kk, k > 0 ? 1u : 0u);
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+              mma_ss(tDP, dDO + off, dVs + off, id_kk, k > 0 ? 1u : 0u);
+            }
+            mma_commit(&ctl->dp_ready);
+            mma_commit(&ctl->v_free[sv]);
+          }
+          if (ok) mma_commit(&ctl->do_free);
+          kc += n_tiles;
+          ++ic;
         }
-        mma_commit(&ctl->dp_ready);
-        mma_commit(&ctl->v_free[sv]);
+        if (ok) mbar_arrive(&ctl->geom_free[slot]);
       }
     }
   } else {
     // -------------------------------------------------------------------- compute warps
-    setmaxnreg_inc<216>();  // 128 x 64 + 256 x 216 <= 384 x 168 (the launch allocation)
+    // Four warps per TMEM lane quadrant, each owning 32 of the tile's 128 key columns.
+    setmaxnreg_inc<104>();  // 128 x 56 + 512 x 104 <= 640 x 96 (the launch allocation)
     const int quad = warp & 3;
-    const int half = (warp - 4) >> 2;       // which 64 key columns of the tile this warp handles
+    const int part = (warp - 4) >> 2;       // which 32 key columns of the tile this warp handles
     const int row = quad * 32 + lane;       // query row inside the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    const bool valid = row < geom->n_valid[0];
-    const int pos = geom->p0[0] + row;
-    int s_p = 0, e_p = 0;
-    if (valid) seq_of(p.cu, p.n_seqs, pos, s_p, e_p);
-    const int hi = valid ? pos : -1;
-    const int lo = valid ? max(s_p, pos - p.window) : 0x7fffffff;
-    const int sink_end = valid ? s_p + p.n_sink : -0x7fffffff;
-    const long long roff = b * p.d_sb + h * p.d_sh + row0 + row;  // rows are padded to whole tiles
-    const float lse2_r = p.lse2[roff];                            // +inf past q_len: P vanishes
-    const float delta_r = p.delta[roff];
     const float sl2 = p.scale_log2;
+    const float mul = p.scale;
     bool ok = true;
-    TileCursor cur;
-    cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int kt0 = cur.kt0 + half * 64;
-      const int span_end = cur.kt_last + 1;
-      const uint32_t tSj = tmem + 128 * (j & 1) + lane_off;
-      ok = mbar_wait(&ctl->s_ready[j & 1], (j >> 1) & 1, err, kErrWaitSoftmax);
+    int n = 0, kc = 0, ic = 0;
+    for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+      const int slot = n & 1;
+      const DqItem w = dq_item(p, n_q_tiles, it);
+      const long long roff = w.b * p.d_sb + w.h * p.d_sh + w.row0 + row;  // rows are padded to whole tiles
+      const float lse2_r = p.lse2[roff];                                  // +inf past q_len: P vanishes
+      const float delta_r = p.delta[roff];
+      ok = mbar_wait(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitSoftmax);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      tc_fence_after();
-      float pr[64];
-      {
-        uint32_t s0[32], s1[32];
-        tmem_ld32(tSj + half * 64, s0);
-        tmem_ld32(tSj + half * 64 + 32, s1);
-        tmem_ld_wait();
+      const QBlockGeom* geom = &ctl->geom[slot];
+      const int n_tiles = geom->n_tiles;
+      const bool valid = row < geom->n_valid[0];
+      const int pos = geom->p0[0] + row;
+      int s_p = 0, e_p = 0;
+      if (valid) seq_of(p.cu, p.n_seqs, pos, s_p, e_p);
+      const int hi = valid ? pos : -1;
+      const int lo = valid ? max(s_p, pos - p.window) : 0x7fffffff;
+      const int sink_end = valid ? s_p + p.n_sink : -0x7fffffff;
+      TileCursor cur;
+      cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int g = kc + j;
+        const int kt0 = cur.kt0 + part * 32;
+        const int span_end = cur.kt_last + 1;
+        const uint32_t tSj = tmem + 128 * (g & 1) + lane_off;
+        ok = mbar_wait(&ctl->s_ready[g & 1], (g >> 1) & 1, err, kErrWaitSoftmax);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        float pr[32];
+        {
+          uint32_t s0[32];
+          tmem_ld32(tSj + part * 32, s0);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          pr[i] = ex2f(fmaf(__uint_as_float(s0[i]), sl2, -lse2_r));
-          pr[i + 32] = ex2f(fmaf(__uint_as_float(s1[i]), sl2, -lse2_r));
+          for (int i = 0; i < 32; ++i) pr[i] = ex2f(fmaf(__uint_as_float(s0[i]), sl2, -lse2_r));
         }
-      }
-      const bool my_mask = !(kt0 >= lo && kt0 + 63 <= hi && kt0 + 63 < span_end);
-      if (__any_sync(0xffffffffu, my_mask)) {
+        const bool my_mask = !(kt0 >= lo && kt0 + 31 <= hi && kt0 + 31 < span_end);
+        if (__any_sync(0xffffffffu, my_mask)) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const int t = kt0 + i;
-          const bool vis = t <= hi && t < span_end && (t >= lo || (t >= s_p && t < sink_end));
-          pr[i] = vis ? pr[i] : 0.f;
+          for (int i = 0; i < 32; ++i) {
+            const int t = kt0 + i;
+            const bool vis = t <= hi && t < span_end && (t >= lo || (t >= s_p && t < sink_end));
+            pr[i] = vis ? pr[i] : 0.f;
+          }
         }
+        ok = mbar_wait(&ctl->dp_ready, g & 1, err, kErrWaitSoftmax);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t dpk[16];
+        {
+          uint32_t d0[32];
+          tmem_ld32(tDP + lane_off + part * 32, d0);
+          tmem_ld_wait();
+          tc_fence_before();
+          mbar_arrive(&ctl->dp_loaded);  // dP of the next tile may overwrite these columns now
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            dpk[i >> 1] = pack2<kBf16>(pr[i] * (__uint_as_float(d0[i]) - delta_r),
+                                       pr[i + 1] * (__uint_as_float(d0[i + 1]) - delta_r));
+          }
+        }
+        // dS (16-bit) goes over the S columns: all four warps of this lane quadrant must have read S
+        bar_sync_quad(1 + quad);
+        tmem_st16(tSj + part * 16, dpk);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&ctl->ds_ready);
+        cursor_next<kTile>(geom, p.span_pos, p.span_len, cur, j + 1 < n_tiles);
       }
-      ok = mbar_wait(&ctl->dp_ready, j & 1, err, kErrWaitSoftmax);
-      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      tc_fence_after();
-      uint32_t dpk[32];
-      {
-        uint32_t d0[32], d1[32];
-        tmem_ld32(tDP + lane_off + half * 64, d0);
-        tmem_ld32(tDP + lane_off + half * 64 + 32, d1);
+
+      // the item's dQ * softmax_scale -> dq; the accumulator is released as soon as it is in registers
+      uint32_t r[32];
+      if (n_tiles > 0) {
+        ok = mbar_wait(&ctl->done, ic & 1, err, kErrWaitEpilogue);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        tmem_ld32(tDQ + lane_off + part * 32, r);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(&ctl->dp_loaded);  // dP of the next tile may overwrite these columns now
+        mbar_arrive(&ctl->dq_drained);
+        kc += n_tiles;
+        ++ic;
+      } else {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          dpk[i >> 1] = pack2<kBf16>(pr[i] * (__uint_as_float(d0[i]) - delta_r),
-                                     pr[i + 1] * (__uint_as_float(d0[i + 1]) - delta_r));
-          dpk[16 + (i >> 1)] = pack2<kBf16>(pr[i + 32] * (__uint_as_float(d1[i]) - delta_r),
-                                            pr[i + 33] * (__uint_as_float(d1[i + 1]) - delta_r));
-        }
+        for (int i = 0; i < 32; ++i) r[i] = 0u;
       }
-      // dS (16-bit) goes over the S columns: both warps of this lane quadrant must have read S
-      bar_sync_pair(1 + quad);
-      tmem_st32(tSj + half * 32, dpk);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&ctl->ds_ready);
-      cursor_next<kTile>(geom, p.span_pos, p.span_len, cur, j + 1 < n_tiles);
-    }
-
-    // epilogue: dQ * softmax_scale -> dq
-    if (ok && n_tiles > 0) ok = mbar_wait(&ctl->done, 0, err, kErrWaitEpilogue);
-    ok = __all_sync(0xffffffffu, ok);
-    tc_fence_after();
-    if (ok && ctl->err == 0) {
-      uint16_t* drow = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_sb + static_cast<long long>(row0 + row) * p.dq_st +
-                       h * p.dq_sh + half * 64;
-      const float mul = p.scale;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        if (n_tiles > 0) {
-          tmem_ld32(tDQ + lane_off + half * 64 + c * 32, r);
-          tmem_ld_wait();
-        } else {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->geom_free[slot]);
+      if (valid) {
+        uint16_t* drow = reinterpret_cast<uint16_t*>(p.dq) + w.b * p.dq_sb +
+                         static_cast<long long>(w.row0 + row) * p.dq_st + w.h * p.dq_sh + part * 32;
+        uint4* dst = reinterpret_cast<uint4*>(drow);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
-        }
-        if (valid) {
-          uint4* dst = reinterpret_cast<uint4*>(drow + c * 32);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
-            o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
-            o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
-            o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
-            dst[v] = o;
-          }
+        for (int v = 0; v < 4; ++v) {
+          uint4 o;
+          o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
+          o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
+          o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
+          o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
+          dst[v] = o;
         }
       }
     }
@@ -328,10 +428,10 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles) {
 
 int launch_dq(const BwdKernelParams& kp, int dtype, cudaStream_t stream) {
   const int n_q_tiles = (kp.q_len + kTile - 1) / kTile;
-  const long long n_cta = static_cast<long long>(n_q_tiles) * kp.hq * kp.batch;
-  if (n_cta <= 0) return RSWA_OK;
-  if (n_cta > 0x7fffffffLL) {
-    set_error("rswa_bwd: too many query tiles (%lld)", n_cta);
+  const long long n_items = static_cast<long long>(n_q_tiles) * kp.hq * kp.batch;
+  if (n_items <= 0) return RSWA_OK;
+  if (n_items > 0x7fffffffLL) {
+    set_error("rswa_bwd: too many query tiles (%lld)", n_items);
     return RSWA_E_ARG;
   }
   auto kern = dtype == RSWA_DTYPE_BF16 ? rswa_dq_kernel<true> : rswa_dq_kernel<false>;
@@ -340,7 +440,9 @@ int launch_dq(const BwdKernelParams& kp, int dtype, cudaStream_t stream) {
     set_error("rswa_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return RSWA_E_CUDA;
   }
-  kern<<<static_cast<unsigned>(n_cta), kDqThreads, kDqSmemBytes, stream>>>(kp, n_q_tiles);
+  // one CTA per SM (shared memory and TMEM allow no more), each striding over the items
+  const long long n_cta = n_items < sm_count() ? n_items : sm_count();
+  kern<<<static_cast<unsigned>(n_cta), kDqThreads, kDqSmemBytes, stream>>>(kp, n_q_tiles, static_cast<int>(n_items));
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("rswa_bwd(dq): launch: %s", cudaGetErrorString(e));

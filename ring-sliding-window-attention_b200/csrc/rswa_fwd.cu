@@ -30,6 +30,7 @@ using namespace tc05;
 namespace {
 
 constexpr int kFwdThreads = 384;   // warp 0 TMA, warps 1-2 MMA (one per query tile), warp 3 idle, warps 4-7 / 8-11 softmax
+constexpr int kMmaPollNs = 0;  // the MMA-issuing threads poll without back-off (they are on the critical path)
 constexpr int kFwdTmemCols = 512;
 constexpr int kFwdSmemTiles = 7 * kTileBytes;  // Q_0, Q_1, K x 3, V x 2
 constexpr int kKStages = 3;
@@ -151,8 +152,8 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       int n_pv = 0;  // products O_w += P_w V issued so far (also the phase of p_ready[w])
       TileCursor cur, nxt;
       cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
-      bool ok = mbar_wait<40>(&ctl->q_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait<40>(&ctl->k_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait<kMmaPollNs>(&ctl->q_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->k_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
         if (tile_active(geom, w, cur, p.n_sink)) {
@@ -170,11 +171,11 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
         const int sv = j & 1, sk = (j + 1) % kKStages;
         nxt = cur;
         cursor_next<kTile>(geom, p.span_pos, p.span_len, nxt, more);
-        ok = mbar_wait<40>(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
-        if (ok && more) ok = mbar_wait<40>(&ctl->k_full[sk], ((j + 1) / kKStages) & 1, err, kErrWaitMma);
+        ok = mbar_wait<kMmaPollNs>(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
+        if (ok && more) ok = mbar_wait<kMmaPollNs>(&ctl->k_full[sk], ((j + 1) / kKStages) & 1, err, kErrWaitMma);
         if (!ok) break;
         if (tile_active(geom, w, cur, p.n_sink)) {
-          ok = mbar_wait<40>(&ctl->p_ready[w], n_pv & 1, err, kErrWaitMma);
+          ok = mbar_wait<kMmaPollNs>(&ctl->p_ready[w], n_pv & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dVs = dV + sv * kTile16;

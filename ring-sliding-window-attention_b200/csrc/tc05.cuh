@@ -236,8 +236,9 @@ __device__ __forceinline__ void mma_commit_w(uint64_t* bar) {
       : "memory");
 }
 // Bounded wait by a whole warp: every lane polls, the result is made uniform.
+template <int kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait_w(uint64_t* bar, uint32_t parity, volatile int* err_flag, int code) {
-  const bool ok = mbar_wait(bar, parity, err_flag, code);
+  const bool ok = mbar_wait<kSleepNs>(bar, parity, err_flag, code);
   return __all_sync(0xffffffffu, ok);
 }
 
