@@ -97,9 +97,9 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       mbar_init(&ctl->do_free[i], 1);
     }
     mbar_init(&ctl->s_ready, 1);
-    mbar_init(&ctl->s_loaded, kComputeThreads);
+    mbar_init(&ctl->s_loaded, kComputeThreads / 32);  // one arrival per compute warp
     mbar_init(&ctl->dp_ready, 1);
-    mbar_init(&ctl->pds_ready, kComputeThreads);
+    mbar_init(&ctl->pds_ready, kComputeThreads / 32);
     mbar_init(&ctl->dv_done, 1);
     mbar_init(&ctl->done, 2);
     ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
@@ -303,7 +303,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         tmem_ld32(tS + lane_off + half * 64 + 32, s1);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(&ctl->s_loaded);  // S^T of the next query tile may overwrite these columns now
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->s_loaded);  // S^T of the next query tile may overwrite these columns now
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
           const float4 la = *reinterpret_cast<const float4*>(lse_s + i);
@@ -360,7 +361,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       tmem_st32(tDS + lane_off + half * 32, dpk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&ctl->pds_ready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->pds_ready);
     }
 
     // epilogue: dK (scaled) and dV for this key tile

@@ -16,12 +16,12 @@
 // every pipeline (K/V rings, S buffers, barrier phases) keeps running across item boundaries, so
 // the fill and drain of one item (first loads, last dQ product, dQ write-out) overlap the next
 // item's loads and products instead of leaving the SM idle.  Roles:
-//   warp 0      TMA producer (Q, dO once per item; K ring of 3, V ring of 2)
-//   warp 1      issues S and dQ products       warp 2   issues dP products
-//   warp 3      computes the key-tile list of the coming item into a two-slot ring
+//   warp 0      key-tile list of each item (two-slot ring) and TMA producer (Q, dO once per item;
+//               K ring of 3, V ring of 2)
+//   warps 1-3   issue the S, dP and dQ products, one warp each
 //   warps 4-19  compute, four warps per TMEM lane quadrant, 32 key columns each
-// Two warps issue MMAs because the issue path, not the tensor pipe, is what one thread saturates
-// first.  TMEM: [0,128) S_0/dS_0, [128,256) S_1/dS_1, [256,384) dP, [384,512) dQ.
+// Three warps issue MMAs because the issue path, not the tensor pipe, is what one thread saturates
+// first: with S and dQ on one thread, that thread was the longest chain of a key tile.  TMEM: [0,128) S_0/dS_0, [128,256) S_1/dS_1, [256,384) dP, [384,512) dQ.
 #include "rswa_common.cuh"
 #include "rswa_tiles.cuh"
 #include "tc05.cuh"
@@ -39,12 +39,13 @@ constexpr int kDqCompute = 512;
 // The MMA-issuing threads poll their barriers without back-off: they sit on the critical path of
 // every key tile, and a sleeping poll was measured slower.
 constexpr int kMmaPollNs = 0;
-constexpr int kDqGeomUsers = 3 + kDqCompute / 32;  // producer, two MMA issuers, one lane per compute warp
+constexpr int kCmpPollNs = 0;
+constexpr int kDqGeomUsers = 4 + kDqCompute / 32;  // producer, three MMA issuers, one lane per compute warp
 
 struct DqCtl {
   uint64_t q_full, do_full, q_free, do_free;
   uint64_t k_full[kDqKStages], v_full[2], k_free[kDqKStages], v_free[2];
-  uint64_t s_ready[2], dp_ready, dp_loaded, ds_ready, done, dq_drained;
+  uint64_t s_ready[2], s_free[2], dp_ready, dp_loaded, ds_ready, done, dq_drained;
   uint64_t geom_full[2], geom_free[2];
   uint32_t tmem_base;
   int err;
@@ -101,14 +102,15 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       mbar_init(&ctl->v_full[i], 1);
       mbar_init(&ctl->v_free[i], 1);
       mbar_init(&ctl->s_ready[i], 1);
+      mbar_init(&ctl->s_free[i], 1);
       mbar_init(&ctl->geom_full[i], 1);
       mbar_init(&ctl->geom_free[i], kDqGeomUsers);
     }
     mbar_init(&ctl->dp_ready, 1);
-    mbar_init(&ctl->dp_loaded, kDqCompute);
-    mbar_init(&ctl->ds_ready, kDqCompute);
+    mbar_init(&ctl->dp_loaded, kDqCompute / 32);  // one arrival per compute warp
+    mbar_init(&ctl->ds_ready, kDqCompute / 32);  // one arrival per compute warp
     mbar_init(&ctl->done, 1);
-    mbar_init(&ctl->dq_drained, kDqCompute);
+    mbar_init(&ctl->dq_drained, kDqCompute / 32);  // one arrival per compute warp
     ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
     mbar_fence_init();
   }
@@ -128,32 +130,25 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
 
   if (warp < 4) {
     setmaxnreg_dec<56>();
-    if (warp == 3 && lane == 0) {
-      // ------------------------------------------------------------------ key-tile lists, one item ahead
-      bool ok = true;
-      int n = 0;
-      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
-        const int slot = n & 1;
-        if (n >= 2) ok = mbar_wait<200>(&ctl->geom_free[slot], ((n >> 1) - 1) & 1, err, kErrWaitProducer);
-        if (!ok) break;
-        const int qt = it % n_q_tiles;
-        // a block of one query tile: the second tile of the geometry stays empty
-        qblock_geometry<kTile>(&ctl->geom[slot], p.cu, p.n_seqs, p.n_spans, p.span_pos, p.span_len, p.q_pos_start,
-                               p.q_len, p.window, p.n_sink, qt, qt + 1);
-        mbar_arrive(&ctl->geom_full[slot]);
-      }
-    } else if (warp == 0 && lane == 0) {
-      // ------------------------------------------------------------------ TMA producer
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------------ key-tile lists + TMA producer
       bool ok = true;
       int n = 0, kc = 0, ic = 0;  // items seen, K/V tiles loaded so far, items with work so far
       for (int it = it0; it < n_items && ok; it += it_step, ++n) {
         const int slot = n & 1;
-        ok = mbar_wait<200>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitProducer);
+        // The list of item n goes into slot n & 1 once every role is done with item n - 2.  This
+        // thread has spare time exactly here: its last loads of the previous item are issued and
+        // the ring stages for this one are still in use.
+        if (n >= 2) ok = mbar_wait<200>(&ctl->geom_free[slot], ((n >> 1) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
-        const QBlockGeom* geom = &ctl->geom[slot];
+        QBlockGeom* geom = &ctl->geom[slot];
+        const DqItem w = dq_item(p, n_q_tiles, it);
+        // a block of one query tile: the second tile of the geometry stays empty
+        qblock_geometry<kTile>(geom, p.cu, p.n_seqs, p.n_spans, p.span_pos, p.span_len, p.q_pos_start, p.q_len,
+                               p.window, p.n_sink, w.qt, w.qt + 1);
+        mbar_arrive(&ctl->geom_full[slot]);
         const int n_tiles = geom->n_tiles;
         if (n_tiles > 0) {
-          const DqItem w = dq_item(p, n_q_tiles, it);
           // Q may be replaced once the last S product of the previous item has read it
           if (ic > 0) ok = mbar_wait<200>(&ctl->q_free, (ic - 1) & 1, err, kErrWaitProducer);
           if (!ok) break;
@@ -190,53 +185,57 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         if (ok) mbar_arrive(&ctl->geom_free[slot]);
       }
     } else if (warp == 1 && lane == 0) {
-      // ------------------------------------------------------------------ MMA issuer 1: S and dQ
+      // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T
       constexpr uint32_t id_kk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
-      constexpr uint32_t id_tn = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
       constexpr uint32_t kTile16 = kTileBytes >> 4;
       const uint64_t dQd = smem_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t dKk = smem_desc_sw128(smem_u32(sK), 16, 1024);        // K as K-major B of S
-      const uint64_t dKm = smem_desc_sw128(smem_u32(sK), kBoxBytes, 1024); // K as MN-major B of dQ
+      const uint64_t dKk = smem_desc_sw128(smem_u32(sK), 16, 1024);  // K as K-major B operand
       bool ok = true;
-      int n = 0, kc = 0, ic = 0;  // kc: key tiles of earlier items, the running index of this item's tile 0
+      int n = 0, kc = 0, ic = 0;  // kc: key tiles of earlier items = running index of this item's tile 0
       for (int it = it0; it < n_items && ok; it += it_step, ++n) {
         const int slot = n & 1;
         ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
         if (!ok) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
-          // S of the item's first tile.  The S buffers keep alternating across items, so the buffer
-          // written here last held dS of a tile whose dQ product this thread issued earlier.
           ok = mbar_wait<kMmaPollNs>(&ctl->q_full, ic & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->k_full[kc % kDqKStages], (kc / kDqKStages) & 1, err, kErrWaitMma);
-          if (!ok) break;
-          tc_fence_after();
-          {
-            const uint64_t dKs = dKk + (kc % kDqKStages) * kTile16;
+          for (int j = 0; j < n_tiles && ok; ++j) {
+            const int g = kc + j;
+            const int sk = g % kDqKStages;
+            ok = mbar_wait<kMmaPollNs>(&ctl->k_full[sk], (g / kDqKStages) & 1, err, kErrWaitMma);
+            // S buffer g & 1 last held dS of tile g - 2: the dQ product that reads it must be complete
+            if (ok && g >= 2) ok = mbar_wait<kMmaPollNs>(&ctl->s_free[g & 1], ((g >> 1) - 1) & 1, err, kErrWaitMma);
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t dKs = dKk + sk * kTile16;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-              mma_ss(tmem + 128 * (kc & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
+              mma_ss(tmem + 128 * (g & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
             }
-            mma_commit(&ctl->s_ready[kc & 1]);
-            if (n_tiles == 1) mma_commit(&ctl->q_free);
+            mma_commit(&ctl->s_ready[g & 1]);
+            if (j + 1 == n_tiles) mma_commit(&ctl->q_free);  // that was the item's last read of Q
           }
+          kc += n_tiles;
+          ++ic;
+        }
+        if (ok) mbar_arrive(&ctl->geom_free[slot]);
+      }
+    } else if (warp == 3 && lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer 3: dQ += dS K
+      constexpr uint32_t id_tn = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
+      constexpr uint32_t kTile16 = kTileBytes >> 4;
+      const uint64_t dKm = smem_desc_sw128(smem_u32(sK), kBoxBytes, 1024);  // K as MN-major B operand
+      bool ok = true;
+      int n = 0, kc = 0, ic = 0;
+      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+        const int slot = n & 1;
+        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
+        if (!ok) break;
+        const int n_tiles = ctl->geom[slot].n_tiles;
+        if (n_tiles > 0) {
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
-            if (j + 1 < n_tiles) {
-              const int sk = (g + 1) % kDqKStages;
-              ok = mbar_wait<kMmaPollNs>(&ctl->k_full[sk], ((g + 1) / kDqKStages) & 1, err, kErrWaitMma);
-              if (!ok) break;
-              tc_fence_after();
-              const uint64_t dKs = dKk + sk * kTile16;
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-                mma_ss(tmem + 128 * ((g + 1) & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
-              }
-              mma_commit(&ctl->s_ready[(g + 1) & 1]);
-              if (j + 2 == n_tiles) mma_commit(&ctl->q_free);  // that was the item's last read of Q
-            }
             ok = mbar_wait<kMmaPollNs>(&ctl->ds_ready, g & 1, err, kErrWaitMma);
             // the first product of an item overwrites dQ: the previous item's must have been read out
             if (ok && j == 0 && ic > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dq_drained, (ic - 1) & 1, err, kErrWaitMma);
@@ -248,6 +247,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
               mma_ts(tDQ, tmem + 128 * (g & 1) + k * 8, dKj + k * 128, id_tn, (j > 0 || k > 0) ? 1u : 0u);
             }
             mma_commit(&ctl->k_free[g % kDqKStages]);
+            mma_commit(&ctl->s_free[g & 1]);
           }
           if (ok) mma_commit(&ctl->done);
           kc += n_tiles;
@@ -312,7 +312,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       const long long roff = w.b * p.d_sb + w.h * p.d_sh + w.row0 + row;  // rows are padded to whole tiles
       const float lse2_r = p.lse2[roff];                                  // +inf past q_len: P vanishes
       const float delta_r = p.delta[roff];
-      ok = mbar_wait(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitSoftmax);
+      ok = mbar_wait<kCmpPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitSoftmax);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       const QBlockGeom* geom = &ctl->geom[slot];
@@ -331,7 +331,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         const int kt0 = cur.kt0 + part * 32;
         const int span_end = cur.kt_last + 1;
         const uint32_t tSj = tmem + 128 * (g & 1) + lane_off;
-        ok = mbar_wait(&ctl->s_ready[g & 1], (g >> 1) & 1, err, kErrWaitSoftmax);
+        ok = mbar_wait<kCmpPollNs>(&ctl->s_ready[g & 1], (g >> 1) & 1, err, kErrWaitSoftmax);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -352,7 +352,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
             pr[i] = vis ? pr[i] : 0.f;
           }
         }
-        ok = mbar_wait(&ctl->dp_ready, g & 1, err, kErrWaitSoftmax);
+        ok = mbar_wait<kCmpPollNs>(&ctl->dp_ready, g & 1, err, kErrWaitSoftmax);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -362,7 +362,8 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
           tmem_ld32(tDP + lane_off + part * 32, d0);
           tmem_ld_wait();
           tc_fence_before();
-          mbar_arrive(&ctl->dp_loaded);  // dP of the next tile may overwrite these columns now
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->dp_loaded);  // dP of the next tile may overwrite these columns now
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
             dpk[i >> 1] = pack2<kBf16>(pr[i] * (__uint_as_float(d0[i]) - delta_r),
@@ -374,7 +375,8 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         tmem_st16(tSj + part * 16, dpk);
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&ctl->ds_ready);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->ds_ready);
         cursor_next<kTile>(geom, p.span_pos, p.span_len, cur, j + 1 < n_tiles);
       }
       if (!ok) break;
@@ -382,14 +384,15 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       // the item's dQ * softmax_scale -> dq; the accumulator is released as soon as it is in registers
       uint32_t r[32];
       if (n_tiles > 0) {
-        ok = mbar_wait(&ctl->done, ic & 1, err, kErrWaitEpilogue);
+        ok = mbar_wait<kCmpPollNs>(&ctl->done, ic & 1, err, kErrWaitEpilogue);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         tmem_ld32(tDQ + lane_off + part * 32, r);
         tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(&ctl->dq_drained);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->dq_drained);
         kc += n_tiles;
         ++ic;
       } else {

@@ -87,7 +87,7 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       mbar_init(&ctl->v_full[i], 1);
       mbar_init(&ctl->v_free[i], 2);
       mbar_init(&ctl->s_ready[i], 1);
-      mbar_init(&ctl->p_ready[i], 128);
+      mbar_init(&ctl->p_ready[i], 4);  // one arrival per softmax warp
       mbar_init(&ctl->pv_done[i], 1);
     }
     ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
@@ -298,7 +298,8 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
         l_sum += l0 + l1;
         tmem_st_wait();
         tc_fence_before();
-        mbar_arrive(&ctl->p_ready[w]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->p_ready[w]);
         ++n_done;
       }
       cursor_next<kTile>(geom, p.span_pos, p.span_len, cur, j + 1 < n_tiles);
