@@ -26,6 +26,7 @@ extern "C" {
 
 #define RSWA_DTYPE_BF16 0
 #define RSWA_DTYPE_FP16 1
+#define RSWA_DTYPE_F32 2 /* only where an entry point says float is accepted */
 
 #define RSWA_OK 0
 #define RSWA_E_ARG (-1)      /* bad shape / stride / alignment / null pointer */
@@ -173,6 +174,29 @@ typedef struct rswa_merge_params {
 } rswa_merge_params_t;
 
 int rswa_merge(const rswa_merge_params_t* p, void* stream);
+
+/* The same merge, in place into the higher-precision accumulators the reference carries between
+ * ring hops: acc_o float [batch,q_len,n_heads,head_dim] (strided views allowed), acc_lse float or
+ * double [batch,n_heads,q_len]; the incoming partial result is bf16, fp16 or float with a float
+ * lse.  The lse is combined in float whatever the accumulator holds, as the reference's kernel does
+ * (ring_swa/ops/merge.py:134-135).  An accumulator lse of -inf gives the incoming result exactly.
+ * head_dim: any multiple of 4.  Replaces merge_attn_out as called from flash_attn_fwd_func
+ * (ring_swa/ops/attn.py:31-36) and from the ring loops (ring_swa/sliding_window/nonvarlen.py:95-150). */
+typedef struct rswa_merge_acc_params {
+  int32_t new_dtype; /* RSWA_DTYPE_BF16, RSWA_DTYPE_FP16 or RSWA_DTYPE_F32 */
+  int32_t lse_f64;   /* accumulator lse: 0 = float, 1 = double */
+  int32_t batch, q_len, n_heads, head_dim;
+  float* acc_o;
+  int64_t acc_stride_b, acc_stride_t, acc_stride_h;
+  const void* new_o;
+  int64_t new_stride_b, new_stride_t, new_stride_h;
+  void* acc_lse;
+  int64_t acc_lse_stride_b, acc_lse_stride_h; /* tokens contiguous */
+  const float* new_lse;
+  int64_t new_lse_stride_b, new_lse_stride_h;
+} rswa_merge_acc_params_t;
+
+int rswa_merge_acc(const rswa_merge_acc_params_t* p, void* stream);
 
 /* acc[b, t, :] += recv[b, t, :] for a [batch, len, row] block: adds the K/V gradients a later
  * rank computed for this rank's trailing tokens (the halo) into the fp32 accumulator.

@@ -111,6 +111,56 @@ __global__ void merge_kernel(const rswa_merge_params_t p, long long n_vec) {
   if (c == 0) p.lse[li] = l;
 }
 
+// In-place merge into a float accumulator (and a float or double lse), the precision the reference
+// carries between ring hops.  One warp per (b, t, h) row, 4 elements per lane and pass.
+// kind of the incoming output: 0 bf16, 1 fp16, 2 float.
+template <int kKind, typename LseT>
+__global__ void merge_acc_kernel(const rswa_merge_acc_params_t p, long long n_rows) {
+  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= n_rows) return;
+  const int h = row % p.n_heads;
+  const long long bt = row / p.n_heads;
+  const int t = bt % p.q_len;
+  const long long b = bt / p.q_len;
+  LseT* la_ptr = static_cast<LseT*>(p.acc_lse) + b * p.acc_lse_stride_b + h * p.acc_lse_stride_h + t;
+  const float la = static_cast<float>(*la_ptr);  // the reference's kernel also reads the double as float
+  const float lb = p.new_lse[b * p.new_lse_stride_b + h * p.new_lse_stride_h + t];
+  const float mx = fmaxf(la, lb);
+  float wa, wb, l;
+  if (mx == -INFINITY) {
+    wa = wb = 0.f;
+    l = -INFINITY;
+  } else {
+    const float ea = __expf(la - mx), eb = __expf(lb - mx);
+    const float inv = 1.f / (ea + eb);
+    wa = ea * inv;
+    wb = eb * inv;
+    l = mx + __logf(ea + eb);
+  }
+  float* ao = p.acc_o + b * p.acc_stride_b + t * p.acc_stride_t + h * p.acc_stride_h;
+  const long long no = b * p.new_stride_b + t * p.new_stride_t + h * p.new_stride_h;
+  for (int c = lane * 4; c < p.head_dim; c += 128) {
+    float4 x = *reinterpret_cast<const float4*>(ao + c);
+    float4 y;
+    if constexpr (kKind == 2) {
+      y = *reinterpret_cast<const float4*>(static_cast<const float*>(p.new_o) + no + c);
+    } else {
+      const uint2 r = *reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p.new_o) + no + c);
+      const float2 r0 = unpack2<kKind == 0>(r.x), r1 = unpack2<kKind == 0>(r.y);
+      y = make_float4(r0.x, r0.y, r1.x, r1.y);
+    }
+    // a zero weight must also silence a non-finite value on that side (an untouched accumulator)
+    x.x = (wa == 0.f ? 0.f : x.x * wa) + (wb == 0.f ? 0.f : y.x * wb);
+    x.y = (wa == 0.f ? 0.f : x.y * wa) + (wb == 0.f ? 0.f : y.y * wb);
+    x.z = (wa == 0.f ? 0.f : x.z * wa) + (wb == 0.f ? 0.f : y.z * wb);
+    x.w = (wa == 0.f ? 0.f : x.w * wa) + (wb == 0.f ? 0.f : y.w * wb);
+    *reinterpret_cast<float4*>(ao + c) = x;
+  }
+  __syncwarp();
+  if (lane == 0) *la_ptr = static_cast<LseT>(l);
+}
+
 // acc += recv; 4 elements per thread.  kind: 0 bf16, 1 fp16, 2 float
 template <int kKind>
 __global__ void halo_acc_kernel(float* __restrict__ acc, long long acc_sb, const void* __restrict__ recv,
@@ -204,6 +254,49 @@ extern "C" int rswa_merge(const rswa_merge_params_t* p, void* stream) {
   kern<<<static_cast<unsigned>((n_vec + threads - 1) / threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
       *p, n_vec);
   return check_launch("rswa_merge");
+}
+
+extern "C" int rswa_merge_acc(const rswa_merge_acc_params_t* p, void* stream) {
+  if (!p || !p->acc_o || !p->new_o || !p->acc_lse || !p->new_lse) {
+    set_error("rswa_merge_acc: null argument");
+    return RSWA_E_ARG;
+  }
+  if (p->new_dtype < 0 || p->new_dtype > RSWA_DTYPE_F32 || (p->lse_f64 != 0 && p->lse_f64 != 1)) {
+    set_error("rswa_merge_acc: new_dtype must be bf16/fp16/float and lse_f64 0 or 1");
+    return RSWA_E_UNSUPPORTED;
+  }
+  if (p->batch <= 0 || p->q_len <= 0 || p->n_heads <= 0 || p->head_dim <= 0 || (p->head_dim % 4)) {
+    set_error("rswa_merge_acc: extents must be positive and head_dim a multiple of 4");
+    return RSWA_E_ARG;
+  }
+  const long long strides[6] = {p->acc_stride_b, p->acc_stride_t, p->acc_stride_h,
+                                p->new_stride_b, p->new_stride_t, p->new_stride_h};
+  for (long long s : strides) {
+    if (s % 4) {
+      set_error("rswa_merge_acc: strides must be multiples of 4 elements");
+      return RSWA_E_ARG;
+    }
+  }
+  const uintptr_t new_mask = p->new_dtype == RSWA_DTYPE_F32 ? 15 : 7;
+  if ((reinterpret_cast<uintptr_t>(p->acc_o) & 15) || (reinterpret_cast<uintptr_t>(p->new_o) & new_mask)) {
+    set_error("rswa_merge_acc: the accumulator must be 16-byte aligned, the incoming output 8- (16-bit) or 16-byte");
+    return RSWA_E_ARG;
+  }
+  const long long n_rows = static_cast<long long>(p->batch) * p->q_len * p->n_heads;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((n_rows * 32 + threads - 1) / threads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int k = p->new_dtype;
+  if (p->lse_f64) {
+    if (k == 0) merge_acc_kernel<0, double><<<blocks, threads, 0, s>>>(*p, n_rows);
+    else if (k == 1) merge_acc_kernel<1, double><<<blocks, threads, 0, s>>>(*p, n_rows);
+    else merge_acc_kernel<2, double><<<blocks, threads, 0, s>>>(*p, n_rows);
+  } else {
+    if (k == 0) merge_acc_kernel<0, float><<<blocks, threads, 0, s>>>(*p, n_rows);
+    else if (k == 1) merge_acc_kernel<1, float><<<blocks, threads, 0, s>>>(*p, n_rows);
+    else merge_acc_kernel<2, float><<<blocks, threads, 0, s>>>(*p, n_rows);
+  }
+  return check_launch("rswa_merge_acc");
 }
 
 extern "C" int rswa_halo_accumulate(float* acc, int64_t acc_stride_b, const void* recv, int64_t recv_stride_b,

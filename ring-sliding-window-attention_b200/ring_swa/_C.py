@@ -76,6 +76,17 @@ class MergeParams(C.Structure):
     ]
 
 
+class MergeAccParams(C.Structure):
+    _fields_ = [
+        ("new_dtype", C.c_int32), ("lse_f64", C.c_int32),
+        ("batch", C.c_int32), ("q_len", C.c_int32), ("n_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("acc_o", C.c_void_p), ("acc_stride_b", C.c_int64), ("acc_stride_t", C.c_int64), ("acc_stride_h", C.c_int64),
+        ("new_o", C.c_void_p), ("new_stride_b", C.c_int64), ("new_stride_t", C.c_int64), ("new_stride_h", C.c_int64),
+        ("acc_lse", C.c_void_p), ("acc_lse_stride_b", C.c_int64), ("acc_lse_stride_h", C.c_int64),
+        ("new_lse", C.c_void_p), ("new_lse_stride_b", C.c_int64), ("new_lse_stride_h", C.c_int64),
+    ]
+
+
 # every symbol include/rswa.h declares, with its signature
 SYMBOLS = {
     "rswa_abi_version": (C.c_int, []),
@@ -86,6 +97,7 @@ SYMBOLS = {
     "rswa_bwd_noalloc": (C.c_int, [C.POINTER(BwdParams), C.c_void_p]),
     "rswa_noalloc_scratch_bytes": (C.c_int64, []),
     "rswa_merge": (C.c_int, [C.POINTER(MergeParams), C.c_void_p]),
+    "rswa_merge_acc": (C.c_int, [C.POINTER(MergeAccParams), C.c_void_p]),
     "rswa_halo_accumulate": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                        C.c_int64, C.c_void_p]),
     "rswa_cast_from_f32": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,

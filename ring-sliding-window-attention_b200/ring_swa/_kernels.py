@@ -276,6 +276,33 @@ def merge(o_a: torch.Tensor, lse_a: torch.Tensor, o_b: torch.Tensor, lse_b: torc
     return out, lse_out
 
 
+def merge_acc(acc_o: torch.Tensor, acc_lse: torch.Tensor, new_o: torch.Tensor, new_lse: torch.Tensor) -> None:
+    """In-place merge of a partial result into a float32 accumulator with a float32 or float64 lse."""
+    if acc_o.dim() != 4 or new_o.shape != acc_o.shape:
+        raise ValueError("merge_acc: outputs must be [B, S, H, D] of one shape")
+    if acc_o.dtype != torch.float32 or acc_o.stride(3) != 1 or new_o.stride(3) != 1:
+        raise ValueError("merge_acc: the accumulator must be float32; head_dim must be contiguous in both")
+    if acc_lse.dtype not in (torch.float32, torch.float64) or new_lse.dtype != torch.float32:
+        raise ValueError("merge_acc: acc lse must be float32/float64 and the incoming lse float32")
+    B, S, H, D = acc_o.shape
+    for l in (acc_lse, new_lse):
+        if l.shape != (B, H, S) or l.stride(2) != 1:
+            raise ValueError("merge_acc: lse tensors must be [B, H, S] with contiguous tokens")
+    p = _C.MergeAccParams()
+    p.new_dtype = _C.DTYPE_F32 if new_o.dtype == torch.float32 else _dtype_code(new_o)
+    p.lse_f64 = 1 if acc_lse.dtype == torch.float64 else 0
+    p.batch, p.q_len, p.n_heads, p.head_dim = B, S, H, D
+    p.acc_o, p.new_o = acc_o.data_ptr(), new_o.data_ptr()
+    p.acc_stride_b, p.acc_stride_t, p.acc_stride_h = acc_o.stride(0), acc_o.stride(1), acc_o.stride(2)
+    p.new_stride_b, p.new_stride_t, p.new_stride_h = new_o.stride(0), new_o.stride(1), new_o.stride(2)
+    p.acc_lse, p.new_lse = acc_lse.data_ptr(), new_lse.data_ptr()
+    p.acc_lse_stride_b, p.acc_lse_stride_h = acc_lse.stride(0), acc_lse.stride(1)
+    p.new_lse_stride_b, p.new_lse_stride_h = new_lse.stride(0), new_lse.stride(1)
+    _C.check(_C.lib().rswa_merge_acc(C.byref(p), _stream()), "rswa_merge_acc")
+    global launch_count
+    launch_count += 1
+
+
 def _rows(t: torch.Tensor) -> Tuple[int, int, int]:
     """(batch, batch stride, contiguous elements per batch row) of a [B, ...] tensor."""
     if t.dim() < 2 or not t[0].is_contiguous():

@@ -35,8 +35,8 @@ def test_struct_sizes_match_the_header():
 #include <stdio.h>
 #include "rswa.h"
 int main(void) {
-  printf("%zu %zu %zu %zu %zu\n", sizeof(rswa_span_t), sizeof(rswa_geom_t), sizeof(rswa_fwd_params_t),
-         sizeof(rswa_bwd_params_t), sizeof(rswa_merge_params_t));
+  printf("%zu %zu %zu %zu %zu %zu\n", sizeof(rswa_span_t), sizeof(rswa_geom_t), sizeof(rswa_fwd_params_t),
+         sizeof(rswa_bwd_params_t), sizeof(rswa_merge_params_t), sizeof(rswa_merge_acc_params_t));
   return 0;
 }
 '''
@@ -47,7 +47,7 @@ int main(void) {
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
         sizes = [int(x) for x in subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()]
     assert sizes == [ctypes.sizeof(_C.Span), ctypes.sizeof(_C.Geom), ctypes.sizeof(_C.FwdParams),
-                     ctypes.sizeof(_C.BwdParams), ctypes.sizeof(_C.MergeParams)]
+                     ctypes.sizeof(_C.BwdParams), ctypes.sizeof(_C.MergeParams), ctypes.sizeof(_C.MergeAccParams)]
 
 
 def test_argument_rejection_without_a_gpu():
@@ -62,6 +62,11 @@ def test_argument_rejection_without_a_gpu():
     # two fp32 rows (delta, scaled lse) per batch row and head, padded to whole 128-query tiles
     assert lib.rswa_bwd_workspace_bytes(1, 130, 2, 128) == 2 * (2 * 256 * 4)
     assert lib.rswa_bwd_workspace_bytes(1, 128, 2, 64) == -1
+    assert lib.rswa_merge_acc(None, None) == -1
+    m = _C.MergeAccParams()
+    m.acc_o = m.new_o = m.acc_lse = m.new_lse = 16
+    m.new_dtype = 7
+    assert lib.rswa_merge_acc(ctypes.byref(m), None) == -2      # unknown dtype of the incoming output
     with pytest.raises(ValueError):
         _C.check(-1, "x")
     with pytest.raises(RuntimeError):
