@@ -51,7 +51,6 @@ constexpr uint32_t kStageTxBytes = kTileBytes + kRowBytes;
 static_assert(sizeof(BwdCtl) <= 256, "control block too large");
 static_assert(kBwdSmemBytes <= 232448, "shared memory budget");
 
-__device__ __forceinline__ void bar_sync_compute() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -134,7 +133,6 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
 
   const uint32_t tmem = ctl->tmem_base;
   const uint32_t tDK = tmem, tDV = tmem + 128, tS = tmem + 256, tB = tmem + 384;
-  const uint32_t tP = tB, tDS = tB + 64;
   volatile int* err = &ctl->err;
   const int qt_first = ctl->qt_first;
   const int n_qt = (ctl->err != 0) ? 0 : ctl->n_qt;
@@ -169,54 +167,56 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         tma_load_4d(sDO + sd * kTileBytes + kBoxBytes, &p.do_map, &ctl->do_full[sd], 64, h, row0, b);
         bulk_load_1d(sDelta + sd * kTile, p.delta + roff, kRowBytes, &ctl->do_full[sd]);
       }
-    } else if (warp == 1 && lane == 0 && n_iter > 0) {
+    } else if (warp == 1 && n_iter > 0) {
       // ------------------------------------------------------------------ MMA issuer 1: S^T and dV
+      // (all 32 lanes run the loop, one elected lane issues: a converged warp keeps its share of the
+      // issue slots when the compute warps beside it are in an FMA-heavy phase, a lone lane does not)
       constexpr int bf = kBf16 ? 1 : 0;
       constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);  // both operands K-major
       constexpr uint32_t id_tn = idesc_f16(128, 128, bf, 0, 1);  // A from TMEM, B MN-major
       const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16, 1024);
       const uint64_t dQk = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t dDOm = smem_desc_sw128(smem_u32(sDO), kBoxBytes, 1024);
-      bool ok = mbar_wait<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->q_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait_w<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->q_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-          mma_ss(tS, dK + off, dQk + off, id_kk, k > 0 ? 1u : 0u);
+          mma_ss_w(tS, dK + off, dQk + off, id_kk, k > 0 ? 1u : 0u);
         }
-        mma_commit(&ctl->s_ready);
+        mma_commit_w(&ctl->s_ready);
       }
       for (int it = 0; it < n_iter && ok; ++it) {
         if (it + 1 < n_iter) {
           // S^T of the next query tile, once every compute warp holds the current one in registers
           const int sq = (it + 1) % kQStages;
-          ok = mbar_wait<kMmaPollNs>(&ctl->q_full[sq], ((it + 1) / kQStages) & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->s_loaded, it & 1, err, kErrWaitMma);
+          ok = mbar_wait_w<kMmaPollNs>(&ctl->q_full[sq], ((it + 1) / kQStages) & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->s_loaded, it & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dQs = dQk + sq * kTile16;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-            mma_ss(tS, dK + off, dQs + off, id_kk, k > 0 ? 1u : 0u);
+            mma_ss_w(tS, dK + off, dQs + off, id_kk, k > 0 ? 1u : 0u);
           }
-          mma_commit(&ctl->s_ready);
+          mma_commit_w(&ctl->s_ready);
         }
-        ok = mbar_wait<kMmaPollNs>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+        ok = mbar_wait_w<kMmaPollNs>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dDOs = dDOm + (it & 1) * kTile16;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {  // dV += P^T dO
-          mma_ts(tDV, tP + k * 8, dDOs + k * 128, id_tn, (it > 0 || k > 0) ? 1u : 0u);
+          mma_ts_w(tDV, tB + (k >> 2) * 64 + (k & 3) * 8, dDOs + k * 128, id_tn, (it > 0 || k > 0) ? 1u : 0u);
         }
-        mma_commit(&ctl->dv_done);
-        mma_commit(&ctl->do_free[it & 1]);
+        mma_commit_w(&ctl->dv_done);
+        mma_commit_w(&ctl->do_free[it & 1]);
       }
-      if (ok) mma_commit(&ctl->done);
-    } else if (warp == 2 && lane == 0 && n_iter > 0) {
+      if (ok) mma_commit_w(&ctl->done);
+    } else if (warp == 2 && n_iter > 0) {
       // ------------------------------------------------------------------ MMA issuer 2: dP^T and dK
       constexpr int bf = kBf16 ? 1 : 0;
       constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);
@@ -224,44 +224,44 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       const uint64_t dV = smem_desc_sw128(smem_u32(sV), 16, 1024);
       const uint64_t dDOk = smem_desc_sw128(smem_u32(sDO), 16, 1024);
       const uint64_t dQm = smem_desc_sw128(smem_u32(sQ), kBoxBytes, 1024);
-      bool ok = mbar_wait<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->do_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait_w<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->do_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-          mma_ss(tB, dV + off, dDOk + off, id_kk, k > 0 ? 1u : 0u);
+          mma_ss_w(tB, dV + off, dDOk + off, id_kk, k > 0 ? 1u : 0u);
         }
-        mma_commit(&ctl->dp_ready);
+        mma_commit_w(&ctl->dp_ready);
       }
       for (int it = 0; it < n_iter && ok; ++it) {
-        ok = mbar_wait<kMmaPollNs>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
+        ok = mbar_wait_w<kMmaPollNs>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
         if (!ok) break;
         tc_fence_after();
         const uint64_t dQs = dQm + (it % kQStages) * kTile16;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {  // dK += dS^T Q
-          mma_ts(tDK, tDS + k * 8, dQs + k * 128, id_tn, (it > 0 || k > 0) ? 1u : 0u);
+          mma_ts_w(tDK, tB + (k >> 2) * 64 + 32 + (k & 3) * 8, dQs + k * 128, id_tn, (it > 0 || k > 0) ? 1u : 0u);
         }
-        mma_commit(&ctl->q_free[it % kQStages]);
+        mma_commit_w(&ctl->q_free[it % kQStages]);
         if (it + 1 < n_iter) {
           // dP^T of the next tile overwrites P^T | dS^T: behind dK (this thread) and dV (the other)
           const int sd = (it + 1) & 1;
-          ok = mbar_wait<kMmaPollNs>(&ctl->do_full[sd], ((it + 1) >> 1) & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->dv_done, it & 1, err, kErrWaitMma);
+          ok = mbar_wait_w<kMmaPollNs>(&ctl->do_full[sd], ((it + 1) >> 1) & 1, err, kErrWaitMma);
+          if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->dv_done, it & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dDOs = dDOk + sd * kTile16;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-            mma_ss(tB, dV + off, dDOs + off, id_kk, k > 0 ? 1u : 0u);
+            mma_ss_w(tB, dV + off, dDOs + off, id_kk, k > 0 ? 1u : 0u);
           }
-          mma_commit(&ctl->dp_ready);
+          mma_commit_w(&ctl->dp_ready);
         }
       }
-      if (ok) mma_commit(&ctl->done);
+      if (ok) mma_commit_w(&ctl->done);
     }
   } else {
     // -------------------------------------------------------------------- compute warps
@@ -354,11 +354,10 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       uint32_t ppk[32];
 #pragma unroll
       for (int i = 0; i < 64; i += 2) ppk[i >> 1] = pack2<kBf16>(pr[i], pr[i + 1]);
-      tc_fence_before();
-      bar_sync_compute();  // every compute warp has read its part of dP^T: its columns can be reused
-      tc_fence_after();
-      tmem_st32(tP + lane_off + half * 32, ppk);
-      tmem_st32(tDS + lane_off + half * 32, dpk);
+      // P^T and dS^T (16-bit) go over the very dP^T columns this warp has just read, so no other
+      // warp has to be waited for: columns [64 half, +32) hold P^T, [64 half + 32, +32) hold dS^T
+      tmem_st32(tB + lane_off + half * 64, ppk);
+      tmem_st32(tB + lane_off + half * 64 + 32, dpk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();

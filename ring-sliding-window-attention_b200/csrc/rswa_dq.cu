@@ -18,7 +18,9 @@
 // item's loads and products instead of leaving the SM idle.  Roles:
 //   warp 0      key-tile list of each item (two-slot ring) and TMA producer (Q, dO once per item;
 //               K ring of 3, V ring of 2)
-//   warps 1-3   issue the S, dP and dQ products, one warp each
+//   warps 1-3   issue the S, dP and dQ products, one warp each (all 32 lanes run the loop and one
+//               elected lane issues: a converged warp is scheduled better than a lone lane when the
+//               compute warps next to it are in an FMA-heavy phase)
 //   warps 4-19  compute, four warps per TMEM lane quadrant, 32 key columns each
 // Three warps issue MMAs because the issue path, not the tensor pipe, is what one thread saturates
 // first: with S and dQ on one thread, that thread was the longest chain of a key tile.  TMEM: [0,128) S_0/dS_0, [128,256) S_1/dS_1, [256,384) dP, [384,512) dQ.
@@ -55,9 +57,6 @@ struct DqCtl {
 constexpr int kDqSmemBytes = kDqSmemTiles + 1024;
 static_assert(sizeof(DqCtl) <= 1024, "control block too large");
 static_assert(kDqSmemBytes <= 232448, "shared memory budget");
-
-// the four compute warps that share a TMEM lane quadrant
-__device__ __forceinline__ void bar_sync_quad(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
 struct DqItem {
   int qt, h, b, hk, row0;
@@ -184,7 +183,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         }
         if (ok) mbar_arrive(&ctl->geom_free[slot]);
       }
-    } else if (warp == 1 && lane == 0) {
+    } else if (warp == 1) {
       // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T
       constexpr uint32_t id_kk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t kTile16 = kTileBytes >> 4;
@@ -194,34 +193,34 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       int n = 0, kc = 0, ic = 0;  // kc: key tiles of earlier items = running index of this item's tile 0
       for (int it = it0; it < n_items && ok; it += it_step, ++n) {
         const int slot = n & 1;
-        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
+        ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
         if (!ok) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
-          ok = mbar_wait<kMmaPollNs>(&ctl->q_full, ic & 1, err, kErrWaitMma);
+          ok = mbar_wait_w<kMmaPollNs>(&ctl->q_full, ic & 1, err, kErrWaitMma);
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
             const int sk = g % kDqKStages;
-            ok = mbar_wait<kMmaPollNs>(&ctl->k_full[sk], (g / kDqKStages) & 1, err, kErrWaitMma);
+            ok = mbar_wait_w<kMmaPollNs>(&ctl->k_full[sk], (g / kDqKStages) & 1, err, kErrWaitMma);
             // S buffer g & 1 last held dS of tile g - 2: the dQ product that reads it must be complete
-            if (ok && g >= 2) ok = mbar_wait<kMmaPollNs>(&ctl->s_free[g & 1], ((g >> 1) - 1) & 1, err, kErrWaitMma);
+            if (ok && g >= 2) ok = mbar_wait_w<kMmaPollNs>(&ctl->s_free[g & 1], ((g >> 1) - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
             tc_fence_after();
             const uint64_t dKs = dKk + sk * kTile16;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-              mma_ss(tmem + 128 * (g & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
+              mma_ss_w(tmem + 128 * (g & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
             }
-            mma_commit(&ctl->s_ready[g & 1]);
-            if (j + 1 == n_tiles) mma_commit(&ctl->q_free);  // that was the item's last read of Q
+            mma_commit_w(&ctl->s_ready[g & 1]);
+            if (j + 1 == n_tiles) mma_commit_w(&ctl->q_free);  // that was the item's last read of Q
           }
           kc += n_tiles;
           ++ic;
         }
-        if (ok) mbar_arrive(&ctl->geom_free[slot]);
+        if (ok && lane == 0) mbar_arrive(&ctl->geom_free[slot]);
       }
-    } else if (warp == 3 && lane == 0) {
+    } else if (warp == 3) {
       // ------------------------------------------------------------------ MMA issuer 3: dQ += dS K
       constexpr uint32_t id_tn = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
       constexpr uint32_t kTile16 = kTileBytes >> 4;
@@ -230,32 +229,33 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       int n = 0, kc = 0, ic = 0;
       for (int it = it0; it < n_items && ok; it += it_step, ++n) {
         const int slot = n & 1;
-        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
+        ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
         if (!ok) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
-            ok = mbar_wait<kMmaPollNs>(&ctl->ds_ready, g & 1, err, kErrWaitMma);
+            ok = mbar_wait_w<kMmaPollNs>(&ctl->ds_ready, g & 1, err, kErrWaitMma);
             // the first product of an item overwrites dQ: the previous item's must have been read out
-            if (ok && j == 0 && ic > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dq_drained, (ic - 1) & 1, err, kErrWaitMma);
+            if (ok && j == 0 && ic > 0) ok = mbar_wait_w<kMmaPollNs>(&ctl->dq_drained, (ic - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
             tc_fence_after();
             const uint64_t dKj = dKm + (g % kDqKStages) * kTile16;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              mma_ts(tDQ, tmem + 128 * (g & 1) + k * 8, dKj + k * 128, id_tn, (j > 0 || k > 0) ? 1u : 0u);
+              mma_ts_w(tDQ, tmem + 128 * (g & 1) + (k >> 1) * 32 + (k & 1) * 8, dKj + k * 128, id_tn,
+                     (j > 0 || k > 0) ? 1u : 0u);
             }
-            mma_commit(&ctl->k_free[g % kDqKStages]);
-            mma_commit(&ctl->s_free[g & 1]);
+            mma_commit_w(&ctl->k_free[g % kDqKStages]);
+            mma_commit_w(&ctl->s_free[g & 1]);
           }
-          if (ok) mma_commit(&ctl->done);
+          if (ok) mma_commit_w(&ctl->done);
           kc += n_tiles;
           ++ic;
         }
-        if (ok) mbar_arrive(&ctl->geom_free[slot]);
+        if (ok && lane == 0) mbar_arrive(&ctl->geom_free[slot]);
       }
-    } else if (warp == 2 && lane == 0) {
+    } else if (warp == 2) {
       // ------------------------------------------------------------------ MMA issuer 2: dP
       constexpr uint32_t id_kk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t kTile16 = kTileBytes >> 4;
@@ -265,33 +265,33 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       int n = 0, kc = 0, ic = 0;
       for (int it = it0; it < n_items && ok; it += it_step, ++n) {
         const int slot = n & 1;
-        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
+        ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
         if (!ok) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
-          ok = mbar_wait<kMmaPollNs>(&ctl->do_full, ic & 1, err, kErrWaitMma);
+          ok = mbar_wait_w<kMmaPollNs>(&ctl->do_full, ic & 1, err, kErrWaitMma);
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
             const int sv = g & 1;
-            ok = mbar_wait<kMmaPollNs>(&ctl->v_full[sv], (g >> 1) & 1, err, kErrWaitMma);
+            ok = mbar_wait_w<kMmaPollNs>(&ctl->v_full[sv], (g >> 1) & 1, err, kErrWaitMma);
             // the compute warps must have read dP of the previous tile out of TMEM
-            if (ok && g > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dp_loaded, (g - 1) & 1, err, kErrWaitMma);
+            if (ok && g > 0) ok = mbar_wait_w<kMmaPollNs>(&ctl->dp_loaded, (g - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
             tc_fence_after();
             const uint64_t dVs = dVk + sv * kTile16;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-              mma_ss(tDP, dDO + off, dVs + off, id_kk, k > 0 ? 1u : 0u);
+              mma_ss_w(tDP, dDO + off, dVs + off, id_kk, k > 0 ? 1u : 0u);
             }
-            mma_commit(&ctl->dp_ready);
-            mma_commit(&ctl->v_free[sv]);
+            mma_commit_w(&ctl->dp_ready);
+            mma_commit_w(&ctl->v_free[sv]);
           }
-          if (ok) mma_commit(&ctl->do_free);
+          if (ok) mma_commit_w(&ctl->do_free);
           kc += n_tiles;
           ++ic;
         }
-        if (ok) mbar_arrive(&ctl->geom_free[slot]);
+        if (ok && lane == 0) mbar_arrive(&ctl->geom_free[slot]);
       }
     }
   } else {
@@ -370,9 +370,9 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
                                        pr[i + 1] * (__uint_as_float(d0[i + 1]) - delta_r));
           }
         }
-        // dS (16-bit) goes over the S columns: all four warps of this lane quadrant must have read S
-        bar_sync_quad(1 + quad);
-        tmem_st16(tSj + part * 16, dpk);
+        // dS (16-bit) goes over the first half of the very S columns this warp has read, so no
+        // other warp has to be waited for: keys [32 part, +32) sit in columns [32 part, +16)
+        tmem_st16(tSj + part * 32, dpk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();

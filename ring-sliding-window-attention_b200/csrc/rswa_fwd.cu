@@ -136,10 +136,12 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
         tma_load_4d(sV + st * kTileBytes + kBoxBytes, &p.v_map[c.span], &ctl->v_full[st], 64, hk, c.tok, b);
         cursor_next<kTile>(geom, p.span_pos, p.span_len, c, j + 1 < n_tiles);
       }
-    } else if ((warp == 1 || warp == 2) && lane == 0 && n_tiles > 0) {
+    } else if ((warp == 1 || warp == 2) && n_tiles > 0) {
       // ------------------------------------------------------------------ MMA issuers
       // One issuing thread per query tile (warps 1 and 2): the two instruction streams are independent
       // (different accumulators) and issuing them from two warps halves the issue cost per product.
+      // All 32 lanes run the loop and one elected lane issues: a converged warp keeps its share of the
+      // issue slots when the softmax warps beside it are in an FMA-heavy phase, a lone lane does not.
       const int w = warp - 1;
       constexpr uint32_t idesc_qk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t idesc_pv = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
@@ -152,38 +154,38 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       int n_pv = 0;  // products O_w += P_w V issued so far (also the phase of p_ready[w])
       TileCursor cur, nxt;
       cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
-      bool ok = mbar_wait<kMmaPollNs>(&ctl->q_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait<kMmaPollNs>(&ctl->k_full[0], 0, err, kErrWaitMma);
+      bool ok = mbar_wait_w<kMmaPollNs>(&ctl->q_full, 0, err, kErrWaitMma);
+      if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->k_full[0], 0, err, kErrWaitMma);
       if (ok) {
         tc_fence_after();
         if (tile_active(geom, w, cur, p.n_sink)) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-            mma_ss(tSw, dQ + off, dK + off, idesc_qk, k > 0 ? 1u : 0u);
+            mma_ss_w(tSw, dQ + off, dK + off, idesc_qk, k > 0 ? 1u : 0u);
           }
-          mma_commit(&ctl->s_ready[w]);
+          mma_commit_w(&ctl->s_ready[w]);
         }
-        mma_commit(&ctl->k_free[0]);
+        mma_commit_w(&ctl->k_free[0]);
       }
       for (int j = 0; j < n_tiles && ok; ++j) {
         const bool more = j + 1 < n_tiles;
         const int sv = j & 1, sk = (j + 1) % kKStages;
         nxt = cur;
         cursor_next<kTile>(geom, p.span_pos, p.span_len, nxt, more);
-        ok = mbar_wait<kMmaPollNs>(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
-        if (ok && more) ok = mbar_wait<kMmaPollNs>(&ctl->k_full[sk], ((j + 1) / kKStages) & 1, err, kErrWaitMma);
+        ok = mbar_wait_w<kMmaPollNs>(&ctl->v_full[sv], (j >> 1) & 1, err, kErrWaitMma);
+        if (ok && more) ok = mbar_wait_w<kMmaPollNs>(&ctl->k_full[sk], ((j + 1) / kKStages) & 1, err, kErrWaitMma);
         if (!ok) break;
         if (tile_active(geom, w, cur, p.n_sink)) {
-          ok = mbar_wait<kMmaPollNs>(&ctl->p_ready[w], n_pv & 1, err, kErrWaitMma);
+          ok = mbar_wait_w<kMmaPollNs>(&ctl->p_ready[w], n_pv & 1, err, kErrWaitMma);
           if (!ok) break;
           tc_fence_after();
           const uint64_t dVs = dV + sv * kTile16;
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            mma_ts(tOw, tSw + k * 8, dVs + k * 128, idesc_pv, (n_pv > 0 || k > 0) ? 1u : 0u);
+            mma_ts_w(tOw, tSw + k * 8, dVs + k * 128, idesc_pv, (n_pv > 0 || k > 0) ? 1u : 0u);
           }
-          mma_commit(&ctl->pv_done[w]);
+          mma_commit_w(&ctl->pv_done[w]);
           ++n_pv;
         }
         if (more && tile_active(geom, w, nxt, p.n_sink)) {
@@ -192,12 +194,12 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-            mma_ss(tSw, dQ + off, dKs + off, idesc_qk, k > 0 ? 1u : 0u);
+            mma_ss_w(tSw, dQ + off, dKs + off, idesc_qk, k > 0 ? 1u : 0u);
           }
-          mma_commit(&ctl->s_ready[w]);
+          mma_commit_w(&ctl->s_ready[w]);
         }
-        mma_commit(&ctl->v_free[sv]);
-        if (more) mma_commit(&ctl->k_free[sk]);
+        mma_commit_w(&ctl->v_free[sv]);
+        if (more) mma_commit_w(&ctl->k_free[sk]);
         cur = nxt;
       }
     }
