@@ -369,8 +369,16 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     if (ok && ctl->err == 0) {
-      const long long off = b * p.dkv_sb[sp] + static_cast<long long>(key0 + row) * p.dkv_st[sp] +
-                            hk * p.dkv_sh[sp] + half * 64;
+      // Each thread holds 64 columns of one key row; stored from registers that would be 32 different
+      // lines per instruction.  The rows therefore pass through shared memory (this warp's 8 KB of
+      // the Q ring, free now that every product has completed; 16-byte chunks XOR-swizzled by row)
+      // and leave as whole 128- or 256-byte row segments, several rows per instruction.
+      uint8_t* stage = sQ + (warp - 4) * 8192;
+      const int n_rows = n_valid_k - quad * 32;  // key rows of this warp that exist
+      const long long off0 = b * p.dkv_sb[sp] + static_cast<long long>(key0 + quad * 32) * p.dkv_st[sp] +
+                             hk * p.dkv_sh[sp] + half * 64;
+      const long long rst = p.dkv_st[sp];
+      const bool f32 = p.grad_fp32[sp] != 0;
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t tsrc = which == 0 ? tDK : tDV;
@@ -386,28 +394,44 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = 0u;
           }
-          if (valid_k) {
-            if (p.grad_fp32[sp]) {
-              float4* dst = reinterpret_cast<float4*>(static_cast<float*>(base) + off + c * 32);
+          if (f32) {
 #pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                dst[v] = make_float4(__uint_as_float(r[v * 4]) * mul, __uint_as_float(r[v * 4 + 1]) * mul,
-                                     __uint_as_float(r[v * 4 + 2]) * mul, __uint_as_float(r[v * 4 + 3]) * mul);
-              }
-            } else {
-              uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + off + c * 32);
+            for (int v = 0; v < 8; ++v) {
+              const float4 o = make_float4(__uint_as_float(r[v * 4]) * mul, __uint_as_float(r[v * 4 + 1]) * mul,
+                                           __uint_as_float(r[v * 4 + 2]) * mul, __uint_as_float(r[v * 4 + 3]) * mul);
+              *reinterpret_cast<float4*>(stage + lane * 256 + (((c * 8 + v) ^ (lane & 15)) << 4)) = o;
+            }
+          } else {
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint4 o;
-                o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
-                o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
-                o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
-                o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
-                dst[v] = o;
-              }
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
+              o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
+              o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
+              o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
+              *reinterpret_cast<uint4*>(stage + lane * 128 + (((c * 4 + v) ^ (lane & 7)) << 4)) = o;
             }
           }
         }
+        __syncwarp();
+        if (f32) {
+          const int ch = lane & 15;
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {  // two 256-byte row segments per instruction
+            const int rr = 2 * i + (lane >> 4);
+            const float4 o = *reinterpret_cast<const float4*>(stage + rr * 256 + ((ch ^ (rr & 15)) << 4));
+            if (rr < n_rows) *reinterpret_cast<float4*>(static_cast<float*>(base) + off0 + rr * rst + ch * 4) = o;
+          }
+        } else {
+          const int ch = lane & 7;
+#pragma unroll 4
+          for (int i = 0; i < 8; ++i) {  // four 128-byte row segments per instruction
+            const int rr = 4 * i + (lane >> 3);
+            const uint4 o = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((ch ^ (rr & 7)) << 4));
+            if (rr < n_rows) *reinterpret_cast<uint4*>(static_cast<uint16_t*>(base) + off0 + rr * rst + ch * 8) = o;
+          }
+        }
+        __syncwarp();  // the staging rows are rewritten for dV
       }
     }
   }

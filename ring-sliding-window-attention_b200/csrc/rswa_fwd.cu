@@ -314,29 +314,45 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
     const bool has = ok && n_done > 0 && l_sum > 0.f;
     const float inv = has ? 1.f / l_sum : 0.f;
     const int grow_q = (tile0 + w) * kTile + row;  // row inside the local q tensor
-    uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<long long>(grow_q) * p.o_st +
-                     h * p.o_sh;
+    if (n_done > 0 && ok) {
+      // The rows go out through shared memory: a thread owns one 256-byte row, so storing from
+      // registers would touch 32 different lines per instruction.  Staged in this warp's quarter of
+      // the (no longer needed) Q tile, 16-byte chunks XOR-swizzled by row, each instruction then
+      // writes two whole rows.  Only this warp touches the quarter: a warp-level sync suffices.
+      uint8_t* stage = sQ + w * kTileBytes + quad * (32 * 256);
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t o[32];
-      if (n_done > 0 && ok) {
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
         tmem_ld32(tO + c * 32, o);
         tmem_ld_wait();
-      }
-      if (valid) {
-        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          uint4 q4 = make_uint4(0, 0, 0, 0);
-          if (has) {
-            q4.x = pack2<kBf16>(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
-            q4.y = pack2<kBf16>(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
-            q4.z = pack2<kBf16>(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
-            q4.w = pack2<kBf16>(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
-          }
-          dst[v] = q4;
+          uint4 q4;
+          q4.x = pack2<kBf16>(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
+          q4.y = pack2<kBf16>(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
+          q4.z = pack2<kBf16>(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
+          q4.w = pack2<kBf16>(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
+          if (!has) q4 = make_uint4(0, 0, 0, 0);  // a row without a visible key
+          *reinterpret_cast<uint4*>(stage + lane * 256 + (((c * 4 + v) ^ (lane & 15)) << 4)) = q4;
         }
       }
+      __syncwarp();
+      const int n_rows = geom->n_valid[w] - quad * 32;  // rows of this warp that exist
+      uint16_t* obase = reinterpret_cast<uint16_t*>(p.out) + b * p.o_sb +
+                        static_cast<long long>((tile0 + w) * kTile + quad * 32) * p.o_st + h * p.o_sh;
+      const int ch = lane & 15;
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const int r = 2 * i + (lane >> 4);
+        const uint4 q4 = *reinterpret_cast<const uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4));
+        if (r < n_rows) *reinterpret_cast<uint4*>(obase + static_cast<long long>(r) * p.o_st + ch * 8) = q4;
+      }
+    } else if (valid) {
+      // no key of the given spans is visible to this query tile: zero rows
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + b * p.o_sb +
+                                            static_cast<long long>(grow_q) * p.o_st + h * p.o_sh);
+#pragma unroll
+      for (int v = 0; v < 16; ++v) dst[v] = make_uint4(0, 0, 0, 0);
     }
     if (valid) {
       p.lse[b * p.l_sb + h * p.l_sh + grow_q] = has ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
