@@ -10,7 +10,7 @@ sequence is sharded over the ranks: by default each rank keeps the 1-GPU chunk (
 
 One JSON line is printed by rank 0.  `value` is timed with inputs resident in HBM; `e2e` adds the
 host->device copy of q, k, v, dO from pinned memory and the device->host copy of out, dq, dk, dv every
-step; `roofline` is the dK/dV backward kernel (the longest one) timed with CUDA events on its stream, `roofline_dq`
+step (three streams: one step's copies overlap the neighbouring steps' compute, none is skipped); `roofline` is the dK/dV backward kernel (the longest one) timed with CUDA events on its stream, `roofline_dq`
 and `roofline_fwd` the other two tensor-core kernels;
 `cpu_baseline` is the dense torch CPU restatement of the reference's test oracle on a bounded slice.
 
@@ -298,22 +298,46 @@ def main():
         h2d = sum(x.numel() * x.element_size() for x in host_in)
         d2h = sum(x.numel() * x.element_size() for x in host_out)
 
-        def e2e_step():
-            for d_, h_ in zip(dev_in, host_in):
-                d_.copy_(h_, non_blocking=True)
-            out, grads = step(dev_in[0].detach(), dev_in[1].detach(), dev_in[2].detach(), dev_in[3])
-            for h_, d_ in zip(host_out, (out,) + grads):
-                h_.copy_(d_, non_blocking=True)
+        # Three streams, two sets of device input buffers: step i's host->device copies run while
+        # step i-1 computes and step i-2's results go back to the host, as an input pipeline that
+        # double-buffers would do it.  Every step still copies all of its inputs in and all of its
+        # results (out, dq, dk, dv) out inside the timed region.
+        main = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        dev_in2 = [dev_in, [torch.empty_like(x) for x in (q, k, v, do)]]
+        free_ev = [None, None]      # inputs of a set may be overwritten once the step that read them is done
+        out_ev = [None]             # the host result buffers are reused by every step
 
-        for _ in range(2):
-            e2e_step()
+        def e2e_step(i):
+            cur = dev_in2[i & 1]
+            with torch.cuda.stream(s_in):
+                if free_ev[i & 1] is not None:
+                    s_in.wait_event(free_ev[i & 1])
+                for d_, h_ in zip(cur, host_in):
+                    d_.copy_(h_, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            main.wait_event(ready)
+            out, grads = step(cur[0].detach(), cur[1].detach(), cur[2].detach(), cur[3])
+            done = torch.cuda.Event()
+            done.record(main)
+            free_ev[i & 1] = done
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for h_, d_ in zip(host_out, (out,) + grads):
+                    d_.record_stream(s_out)
+                    h_.copy_(d_, non_blocking=True)
+
+        for i in range(2):
+            e2e_step(i)
         sync_all()
-        n_e2e = max(3, min(args.steps, 10))
+        n_e2e = max(4, min(args.steps, 10))
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        f1.record()
+        f0.record(main)
+        for i in range(n_e2e):
+            e2e_step(i)
+        main.wait_stream(s_out)     # the last results are on the host when the clock stops
+        f1.record(main)
         sync_all()
         e2e_ms = f0.elapsed_time(f1) / n_e2e
     clocks = sampler.stop() if sampler else None
