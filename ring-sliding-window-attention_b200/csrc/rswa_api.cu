@@ -44,6 +44,10 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int batch, int 
                   long long sb, long long st, long long sh) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return RSWA_E_CUDA;
+  // The encoder is a driver entry point and wants a context current on the calling thread.  A thread
+  // that has made no runtime call yet (an autograd worker calling the backward first) may have none:
+  // this binds the primary context of the thread's current device and costs nothing afterwards.
+  cudaFree(nullptr);
   if (base == nullptr || (reinterpret_cast<uintptr_t>(base) & 15) != 0) {
     set_error("tensor base pointer must be non-null and 16-byte aligned");
     return RSWA_E_ARG;

@@ -270,3 +270,35 @@ def test_argument_errors_are_raised_not_faulted():
         K.fwd(k.float(), [K.KVSpan(k, k, 0)], 10, 0, 0.1)
     with pytest.raises(RuntimeError, match="no CPU path"):
         K.fwd(k.cpu(), [K.KVSpan(k.cpu(), k.cpu(), 0)], 10, 0, 0.1)
+
+
+def test_backward_called_first_from_a_fresh_thread():
+    """The autograd engine calls the backward from a worker thread that may not have made any CUDA call
+    of its own yet; building the tensor maps there must still work (the library binds a context itself)."""
+    import threading
+    K = _K()
+    dev = torch.device("cuda")
+    B, S, H, W = 1, 256, 2, 100
+    q, k, v, do = (randn_bf16(B, S, H, D, seed=70 + i).to(dev) for i in range(4))
+    out, lse = K.fwd(q, [K.KVSpan(k, v, 0)], W, 0, D ** -0.5)
+    ref = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    K.bwd(q, [K.KVSpan(k, v, 0, dk=ref[1], dv=ref[2])], out, lse, do, ref[0], W, 0, D ** -0.5)
+    got = [torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)]
+    ws = K.bwd_workspace(q)
+    stream = torch.cuda.current_stream()
+    err = []
+
+    def run():
+        try:
+            with torch.cuda.stream(stream):
+                K.bwd(q, [K.KVSpan(k, v, 0, dk=got[1], dv=got[2])], out, lse, do, got[0], W, 0, D ** -0.5, workspace=ws)
+        except Exception as e:  # noqa: BLE001 - reported below
+            err.append(e)
+
+    th = threading.Thread(target=run)
+    th.start()
+    th.join()
+    assert not err, err
+    torch.cuda.synchronize()
+    for a, b in zip(got, ref):
+        assert torch.equal(a, b)      # the backward is deterministic
