@@ -20,7 +20,9 @@
 // current one out of TMEM, dP^T of the next tile right behind dV/dK of the current one, so the
 // exponentials of tile i+1 overlap the products of tile i.  Q tiles travel through a 3-stage ring
 // (they are needed one tile ahead), dO tiles through a 2-stage ring.  Two warps issue MMAs.
-// TMEM columns: [0,128) dK, [128,256) dV, [256,384) S^T, [384,512) dP^T then P^T | dS^T.
+// TMEM columns: [0,128) dK, [128,256) dV, [256,384) S^T, [384,512) dP^T, over which each compute
+// warp writes P^T and dS^T of the 64 query columns it has just read (P^T in the first 32 of its 64
+// columns, dS^T in the other 32).  dK and dV leave through shared memory as whole row segments.
 #include "rswa_common.cuh"
 #include "tc05.cuh"
 
@@ -64,8 +66,15 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   float* sDelta = sLse + kQStages * kTile;                       // [2][128], travels with dO
   BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + kBwdSmemTiles + (kQStages + 2) * kRowBytes);
 
-  // a device-side error was already reported on this stream: do not pile further time-outs on it
-  if (__syncthreads_or(*reinterpret_cast<volatile int*>(p.status) != 0)) return;
+  // Has a device-side error already been reported on this stream?  Then this CTA does no work (no
+  // further time-outs piled on the first).  The word is read now and looked at after the set-up
+  // below, so that its latency is not paid at the head of every CTA.
+  int prior = 0;
+  if (threadIdx.x == 0) {
+    prior = *reinterpret_cast<volatile int*>(p.status);
+    prefetch_tmap(&p.q_map);
+    prefetch_tmap(&p.do_map);
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -101,8 +110,15 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     mbar_init(&ctl->pds_ready, kComputeThreads / 32);
     mbar_init(&ctl->dv_done, 1);
     mbar_init(&ctl->done, 2);
-    ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
     mbar_fence_init();
+    // K and V of this tile depend on nothing computed below: they are on their way while the rest
+    // of the set-up runs (the CTA waits for them before it exits even if it has no work)
+    mbar_expect_tx(&ctl->kv_full, 2 * kTileBytes);
+    tma_load_4d(sK, &p.k_map[sp], &ctl->kv_full, 0, hk, key0, b);
+    tma_load_4d(sK + kBoxBytes, &p.k_map[sp], &ctl->kv_full, 64, hk, key0, b);
+    tma_load_4d(sV, &p.v_map[sp], &ctl->kv_full, 0, hk, key0, b);
+    tma_load_4d(sV + kBoxBytes, &p.v_map[sp], &ctl->kv_full, 64, hk, key0, b);
+    ctl->err = (smem_u32(smem) & 1023u) ? 199 : prior;
     // query tiles that can see at least one key of this tile
     const int t_last = t0 + n_valid_k - 1;
     int s_last, e_last;
@@ -143,11 +159,6 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     setmaxnreg_dec<64>();
     if (warp == 0 && lane == 0 && n_iter > 0) {
       // ------------------------------------------------------------------ TMA producer
-      mbar_expect_tx(&ctl->kv_full, 2 * kTileBytes);
-      tma_load_4d(sK, &p.k_map[sp], &ctl->kv_full, 0, hk, key0, b);
-      tma_load_4d(sK + kBoxBytes, &p.k_map[sp], &ctl->kv_full, 64, hk, key0, b);
-      tma_load_4d(sV, &p.v_map[sp], &ctl->kv_full, 0, hk, key0, b);
-      tma_load_4d(sV + kBoxBytes, &p.v_map[sp], &ctl->kv_full, 64, hk, key0, b);
       bool ok = true;
       for (int it = 0; it < n_iter && ok; ++it) {
         const int sq = it % kQStages, sd = it & 1;
@@ -436,6 +447,8 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     }
   }
 
+  // no product waited for K and V: their copy must still have landed before the CTA goes away
+  if (threadIdx.x == 0 && n_iter == 0) mbar_wait<200>(&ctl->kv_full, 0, err, kErrWaitProducer);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {

@@ -1,18 +1,20 @@
 // Forward kernel: banded (sliding-window + sink) softmax attention on the sm_100a tensor cores.
 //
 // One CTA owns two consecutive 128-row query tiles of one head and walks the key tiles either of
-// them can see.  Two softmax warp groups (one per query tile) work in ping-pong against a single
-// MMA-issuing thread, so that the tensor cores compute one tile's products while the other tile's
-// exponentials run:
+// them can see.  Two softmax warp groups (one per query tile) work in ping-pong against two
+// MMA-issuing warps (one per query tile), so that the tensor cores compute one tile's products
+// while the other tile's exponentials run:
 //
 //   S_w = Q_w K^T      tcgen05.mma, both operands in shared memory (K-major), accumulator in TMEM
 //   P_w = softmax      warp group w: one query row per thread, whole S row in registers, P written
 //                      back (16-bit) over the same TMEM columns
 //   O_w += P_w V       tcgen05.mma, A = P_w from TMEM, B = V from shared memory (MN-major)
 //
-// The MMA thread issues S_w of the NEXT key tile right behind O_w += P_w V of the current one
-// (tcgen05.mma instructions of one thread execute in issue order, so the overwrite of P_w's columns
-// cannot overtake its last reader).  K and V tiles travel through two-stage TMA rings.
+// The issuing warp of tile w issues S_w of the NEXT key tile right behind O_w += P_w V of the
+// current one (tcgen05.mma instructions of one thread execute in issue order, so the overwrite of
+// P_w's columns cannot overtake its last reader).  K tiles travel through a three-stage TMA ring
+// (they are consumed one key tile ahead of V), V tiles through a two-stage ring.  The finished
+// rows leave through shared memory so that every store instruction writes whole rows.
 // TMEM: [0,128) S_0/P_0, [128,256) S_1/P_1, [256,384) O_0, [384,512) O_1.
 //
 // Key tiles that no row of the block can see are never loaded (rswa_tiles.cuh); a query tile skips
