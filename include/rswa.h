@@ -100,7 +100,8 @@ int rswa_fwd(const rswa_fwd_params_t* p, void* stream);
  * carries dk/dv pointers (spans with both NULL take part in dq only), a query-stationary one
  * writes dq summed over all spans of the call when FINISH is set.  Nothing is reduced through
  * global memory, so the result is deterministic.  `workspace` is rswa_bwd_workspace_bytes() of
- * device memory (two fp32 rows per batch row and head: delta and the scaled lse, filled by INIT).
+ * device memory (two fp32 rows per batch row and head: delta and the scaled lse, filled by INIT; plus
+ * 256 bytes for the work counter of the dQ kernel, which the call itself resets on the stream).
  * One call with flags INIT|FINISH does a whole backward.  A ring rank calls it twice with the same
  * workspace: INIT with the received spans only (their gradients can leave early), then FINISH with
  * every span, gradient pointers on the local one only.

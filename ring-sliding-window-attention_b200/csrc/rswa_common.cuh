@@ -67,6 +67,7 @@ struct BwdKernelParams {
   const float* delta;
   long long d_sb, d_sh;
   void* dq;  // [batch, q_len, hq, 128], 16-bit, written by the dQ kernel
+  int* dq_counter;  // work counter of the dQ kernel, zeroed before its launch
   long long dq_sb, dq_st, dq_sh;
   int* status;
 };

@@ -12,7 +12,7 @@
 // P is recomputed from the final log-sum-exp, so the result is exact for any set of spans
 // (the property the reference's per-hop backward relies on, ring_swa/ops/attn.py:63-126).
 //
-// The kernel is persistent: one CTA per SM takes items blockIdx.x, blockIdx.x + gridDim.x, ... and
+// The kernel is persistent: one CTA per SM keeps taking items from a counter in global memory and
 // every pipeline (K/V rings, S buffers, barrier phases) keeps running across item boundaries, so
 // the fill and drain of one item (first loads, last dQ product, dQ write-out) overlap the next
 // item's loads and products instead of leaving the SM idle.  Roles:
@@ -51,6 +51,7 @@ struct DqCtl {
   uint64_t geom_full[2], geom_free[2];
   uint32_t tmem_base;
   int err;
+  int item[2];  // work item of each geometry slot, -1: no more work
   QBlockGeom geom[2];
 };
 
@@ -124,8 +125,10 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
   const uint32_t tmem = ctl->tmem_base;
   const uint32_t tDP = tmem + 256, tDQ = tmem + 384;
   volatile int* err = &ctl->err;
-  const int it0 = (ctl->err != 0) ? n_items : static_cast<int>(blockIdx.x);
-  const int it_step = static_cast<int>(gridDim.x);
+  // Items are handed out through a counter in global memory rather than by a fixed stride: a CTA
+  // whose SM is busy with another kernel (a collective of the ring, say) starts late and simply takes
+  // fewer items, instead of leaving its whole share for the end.
+  const int n_work = (ctl->err != 0) ? 0 : n_items;
 
   if (warp < 4) {
     setmaxnreg_dec<56>();
@@ -133,13 +136,20 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       // ------------------------------------------------------------------ key-tile lists + TMA producer
       bool ok = true;
       int n = 0, kc = 0, ic = 0;  // items seen, K/V tiles loaded so far, items with work so far
-      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+      for (;; ++n) {
         const int slot = n & 1;
         // The list of item n goes into slot n & 1 once every role is done with item n - 2.  This
         // thread has spare time exactly here: its last loads of the previous item are issued and
         // the ring stages for this one are still in use.
         if (n >= 2) ok = mbar_wait<200>(&ctl->geom_free[slot], ((n >> 1) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
+        const int it = n_work > 0 ? atomicAdd(p.dq_counter, 1) : n_work;
+        if (it >= n_work) {  // tell every role that the work has run out
+          ctl->item[slot] = -1;
+          mbar_arrive(&ctl->geom_full[slot]);
+          break;
+        }
+        ctl->item[slot] = it;
         QBlockGeom* geom = &ctl->geom[slot];
         const DqItem w = dq_item(p, n_q_tiles, it);
         // a block of one query tile: the second tile of the geometry stays empty
@@ -191,10 +201,10 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       const uint64_t dKk = smem_desc_sw128(smem_u32(sK), 16, 1024);  // K as K-major B operand
       bool ok = true;
       int n = 0, kc = 0, ic = 0;  // kc: key tiles of earlier items = running index of this item's tile 0
-      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+      for (;; ++n) {
         const int slot = n & 1;
         ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
-        if (!ok) break;
+        if (!ok || ctl->item[slot] < 0) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
           ok = mbar_wait_w<kMmaPollNs>(&ctl->q_full, ic & 1, err, kErrWaitMma);
@@ -227,10 +237,10 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       const uint64_t dKm = smem_desc_sw128(smem_u32(sK), kBoxBytes, 1024);  // K as MN-major B operand
       bool ok = true;
       int n = 0, kc = 0, ic = 0;
-      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+      for (;; ++n) {
         const int slot = n & 1;
         ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
-        if (!ok) break;
+        if (!ok || ctl->item[slot] < 0) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
           for (int j = 0; j < n_tiles && ok; ++j) {
@@ -263,10 +273,10 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       const uint64_t dVk = smem_desc_sw128(smem_u32(sV), 16, 1024);
       bool ok = true;
       int n = 0, kc = 0, ic = 0;
-      for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+      for (;; ++n) {
         const int slot = n & 1;
         ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
-        if (!ok) break;
+        if (!ok || ctl->item[slot] < 0) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
           ok = mbar_wait_w<kMmaPollNs>(&ctl->do_full, ic & 1, err, kErrWaitMma);
@@ -306,15 +316,17 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
     const float mul = p.scale;
     bool ok = true;
     int n = 0, kc = 0, ic = 0;
-    for (int it = it0; it < n_items && ok; it += it_step, ++n) {
+    for (;; ++n) {
       const int slot = n & 1;
+      ok = mbar_wait<kCmpPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitSoftmax);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int it = ctl->item[slot];
+      if (it < 0) break;
       const DqItem w = dq_item(p, n_q_tiles, it);
       const long long roff = w.b * p.d_sb + w.h * p.d_sh + w.row0 + row;  // rows are padded to whole tiles
       const float lse2_r = p.lse2[roff];                                  // +inf past q_len: P vanishes
       const float delta_r = p.delta[roff];
-      ok = mbar_wait<kCmpPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitSoftmax);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
       const QBlockGeom* geom = &ctl->geom[slot];
       const int n_tiles = geom->n_tiles;
       const bool valid = row < geom->n_valid[0];

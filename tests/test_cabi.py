@@ -60,7 +60,7 @@ def test_argument_rejection_without_a_gpu():
     assert lib.rswa_fwd(ctypes.byref(p), None) == -2          # unsupported head_dim
     assert b"head_dim" in lib.rswa_last_error()
     # two fp32 rows (delta, scaled lse) per batch row and head, padded to whole 128-query tiles
-    assert lib.rswa_bwd_workspace_bytes(1, 130, 2, 128) == 2 * (2 * 256 * 4)
+    assert lib.rswa_bwd_workspace_bytes(1, 130, 2, 128) == 2 * (2 * 256 * 4) + 256     # + the dQ work counter
     assert lib.rswa_bwd_workspace_bytes(1, 128, 2, 64) == -1
     assert lib.rswa_merge_acc(None, None) == -1
     m = _C.MergeAccParams()
