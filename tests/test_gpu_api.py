@@ -150,3 +150,88 @@ def test_full_size_config_spot_blocks():
         assert_close(f"dq[{a}:{b}]", q.grad[:, a:b, heads], rdq)
         assert_close(f"dk[{a}:{b}]", k.grad[:, a:b, heads], rdk)
         assert_close(f"dv[{a}:{b}]", v.grad[:, a:b, heads], rdv)
+
+
+def _region_reference(q, k, v, do, W, n_sink, cu, a, b, q_heads):
+    """fp32 torch attention, on the GPU, of the queries [a - 0, b + W) against the keys [a - W, b + W)
+    (plus the sink tokens of the sequence, at their own positions), masked by the oracle's band_mask
+    on GLOBAL positions.  out/dq of queries [a, b) and dk/dv of keys [a, b) then equal the values of
+    the whole problem: every such query has its complete window, every such key all its queries.
+    q_heads must be the query heads of ONE kv head.  Returns out, lse, dq (rows [a, b)), dk, dv (keys [a, b))."""
+    from oracle.dense_attn import band_mask
+    T = q.shape[1]
+    g = q.shape[2] // k.shape[2]
+    kh = q_heads[0] // g
+    assert all(h // g == kh for h in q_heads)
+    lo, hi = max(0, a - W), min(T, b + W)
+    q_pos = torch.arange(a, hi)
+    key_idx = torch.arange(lo, hi)
+    if n_sink:
+        starts = [0] if cu is None else cu[:-1]
+        s0 = max(s for s in starts if s <= a)
+        sink = torch.arange(s0, min(s0 + n_sink, lo))       # sink tokens that lie outside the window range
+        key_idx = torch.cat([sink, key_idx])
+    mask = band_mask(q_pos, key_idx, W, n_sink, cu).to(q.device)
+    dev_idx = key_idx.to(q.device)
+    qs = q[:, a:hi, q_heads].float().requires_grad_(True)
+    ks = k[:, dev_idx][:, :, kh].float().requires_grad_(True)
+    vs = v[:, dev_idx][:, :, kh].float().requires_grad_(True)
+    s = torch.einsum("bihd,bjd->bhij", qs, ks) * (D ** -0.5)
+    s = s.masked_fill(~mask[None, None], float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    o = torch.einsum("bhij,bjd->bihd", torch.softmax(s, -1), vs)
+    o.backward(do[:, a:hi, q_heads].float())
+    n_lead = key_idx.numel() - (hi - lo)                    # sink rows in front
+    ksl = slice(n_lead + a - lo, n_lead + b - lo)
+    return o.detach()[:, : b - a], lse[:, :, : b - a], qs.grad[:, : b - a], ks.grad[:, ksl], vs.grad[:, ksl]
+
+
+@pytest.mark.parametrize("name", ["cfg3", "cfg4"])
+def test_full_size_varlen_and_sink_spot_blocks(name):
+    """BASELINE configurations 3 (packed sequences, 32/8 heads, W=4096, 65536 tokens) and 4 (sink + window,
+    32/8 heads, W=8192, 131072 tokens) at full size on one GPU: blocks of out, dq, dk, dv against fp32 torch
+    on the same tokens; the backward is deterministic, so a second run must agree bit for bit."""
+    import ring_swa
+    dev = torch.device("cuda")
+    Hq, Hkv = 32, 8
+    if name == "cfg3":
+        lens = [7204, 3978, 14070, 10318, 13142, 12634, 4190]
+        cu = [0]
+        for L in lens:
+            cu.append(cu[-1] + L)
+        T, W, n_sink, seed = 65536, 4096, 0, 2
+        blocks = [(7100, 7300, [4, 5, 6, 7]), (30000, 30160, [28, 29, 30, 31]), (65400, 65536, [0, 1, 2, 3])]
+    else:
+        cu = None
+        T, W, n_sink, seed = 131072, 8192, 1, 3
+        blocks = [(0, 128, [0, 1, 2, 3]), (50000, 50128, [12, 13, 14, 15]), (130944, 131072, [28, 29, 30, 31])]
+    g = torch.Generator(device=dev).manual_seed(seed)
+    q, k, v, do = (torch.randn(1, T, h, D, device=dev, generator=g).bfloat16() for h in (Hq, Hkv, Hkv, Hq))
+
+    def run():
+        qq, kk, vv = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+        if name == "cfg3":
+            out = ring_swa.ring_sliding_window_attn_varlen(
+                qq[0], kk[0], vv[0], W, torch.tensor(cu, dtype=torch.int32, device=dev), cp_size=1)[None]
+        else:
+            out = ring_swa.ring_streaming_llm_attn(qq, kk, vv, W)
+        out.backward(do)
+        return out.detach(), qq.grad, kk.grad, vv.grad
+
+    got = run()
+    again = run()
+    from ring_swa._kernels import check_device_status
+    check_device_status()
+    for x, y in zip(got, again):
+        assert torch.equal(x, y)
+    out, dq, dk, dv = got
+    for a, b, heads in blocks:
+        ro, _rl, rdq, rdk, rdv = _region_reference(q, k, v, do, W, n_sink, cu, a, b, heads)
+        kh = [heads[0] // (Hq // Hkv)]
+        assert_close(f"out[{a}:{b}]", out[:, a:b, heads], ro)
+        assert_close(f"dq[{a}:{b}]", dq[:, a:b, heads], rdq)
+        lo_k = max(a, n_sink) if a == 0 else a           # the sink key's own gradient gathers every later query
+        sl = slice(lo_k - a, b - a)
+        assert_close(f"dk[{lo_k}:{b}]", dk[:, lo_k:b, kh][:, :, 0], rdk[:, sl])
+        assert_close(f"dv[{lo_k}:{b}]", dv[:, lo_k:b, kh][:, :, 0], rdv[:, sl])
+        torch.cuda.empty_cache()
