@@ -46,8 +46,13 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int batch, int 
   if (!enc) return RSWA_E_CUDA;
   // The encoder is a driver entry point and wants a context current on the calling thread.  A thread
   // that has made no runtime call yet (an autograd worker calling the backward first) may have none:
-  // this binds the primary context of the thread's current device and costs nothing afterwards.
-  cudaFree(nullptr);
+  // once per thread, bind the primary context of the thread's current device.  (Once, because the
+  // call synchronises and must not recur inside a stream capture.)
+  static thread_local bool t_context_bound = false;
+  if (!t_context_bound) {
+    cudaFree(nullptr);
+    t_context_bound = true;
+  }
   if (base == nullptr || (reinterpret_cast<uintptr_t>(base) & 15) != 0) {
     set_error("tensor base pointer must be non-null and 16-byte aligned");
     return RSWA_E_ARG;
