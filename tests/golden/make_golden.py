@@ -1,9 +1,9 @@
 """Generates the golden vectors under tests/golden/ from the REFERENCE's own code.
 
-Run once, in a container that has the reference checked out (default
-``/root/reference`` or ``$RSWA_REFERENCE``)::
+Run once, on a machine that has the reference project checked out, with its
+location in ``$RSWA_REFERENCE``::
 
-    python tests/golden/make_golden.py
+    RSWA_REFERENCE=<checkout of ring-sliding-window-attention> python tests/golden/make_golden.py
 
 Two sources, both executed on CPU:
 
@@ -34,7 +34,9 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-REF = os.environ.get("RSWA_REFERENCE", "/root/reference")
+REF = os.environ.get("RSWA_REFERENCE", "")
+if not REF or not os.path.isdir(os.path.join(REF, "ring_swa")):
+    raise SystemExit("set RSWA_REFERENCE to a checkout of the reference project (it must contain ring_swa/)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
