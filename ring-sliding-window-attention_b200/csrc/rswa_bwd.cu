@@ -337,34 +337,38 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
           pr[i] = (pq >= t && pq <= p_hi) ? pr[i] : 0.f;
         }
       }
-      // dS^T = P^T * (dP^T - delta)
+      // Everything that does not need dP^T happens before the wait for it (the wait is on the loop
+      // that bounds the kernel): P^T is packed, and -P^T * delta is formed so that one FMA per
+      // element remains afterwards: dS^T = P^T * dP^T - P^T * delta.
+      uint32_t ppk[32];
+#pragma unroll
+      for (int i = 0; i < 64; i += 2) ppk[i >> 1] = pack2<kBf16>(pr[i], pr[i + 1]);
+      float npd[64];
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 da = *reinterpret_cast<const float4*>(del_s + i);
+        const float4 db = *reinterpret_cast<const float4*>(del_s + i + 32);
+        npd[i + 0] = -pr[i + 0] * da.x, npd[i + 1] = -pr[i + 1] * da.y;
+        npd[i + 2] = -pr[i + 2] * da.z, npd[i + 3] = -pr[i + 3] * da.w;
+        npd[i + 32] = -pr[i + 32] * db.x, npd[i + 33] = -pr[i + 33] * db.y;
+        npd[i + 34] = -pr[i + 34] * db.z, npd[i + 35] = -pr[i + 35] * db.w;
+      }
       ok = mbar_wait(&ctl->dp_ready, it & 1, err, kErrWaitSoftmax);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       uint32_t dpk[32];
-      {
-        uint32_t d0[32], d1[32];
-        tmem_ld32(tB + lane_off + half * 64, d0);
-        tmem_ld32(tB + lane_off + half * 64 + 32, d1);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t d[32];
+        tmem_ld32(tB + lane_off + half * 64 + c * 32, d);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float4 da = *reinterpret_cast<const float4*>(del_s + i);
-          const float4 db = *reinterpret_cast<const float4*>(del_s + i + 32);
-          dpk[(i >> 1) + 0] = pack2<kBf16>(pr[i + 0] * (__uint_as_float(d0[i + 0]) - da.x),
-                                           pr[i + 1] * (__uint_as_float(d0[i + 1]) - da.y));
-          dpk[(i >> 1) + 1] = pack2<kBf16>(pr[i + 2] * (__uint_as_float(d0[i + 2]) - da.z),
-                                           pr[i + 3] * (__uint_as_float(d0[i + 3]) - da.w));
-          dpk[(i >> 1) + 16] = pack2<kBf16>(pr[i + 32] * (__uint_as_float(d1[i + 0]) - db.x),
-                                            pr[i + 33] * (__uint_as_float(d1[i + 1]) - db.y));
-          dpk[(i >> 1) + 17] = pack2<kBf16>(pr[i + 34] * (__uint_as_float(d1[i + 2]) - db.z),
-                                            pr[i + 35] * (__uint_as_float(d1[i + 3]) - db.w));
+        for (int i = 0; i < 32; i += 2) {
+          dpk[c * 16 + (i >> 1)] = pack2<kBf16>(fmaf(pr[c * 32 + i], __uint_as_float(d[i]), npd[c * 32 + i]),
+                                                fmaf(pr[c * 32 + i + 1], __uint_as_float(d[i + 1]), npd[c * 32 + i + 1]));
         }
       }
-      uint32_t ppk[32];
-#pragma unroll
-      for (int i = 0; i < 64; i += 2) ppk[i >> 1] = pack2<kBf16>(pr[i], pr[i + 1]);
       // P^T and dS^T (16-bit) go over the very dP^T columns this warp has just read, so no other
       // warp has to be waited for: columns [64 half, +32) hold P^T, [64 half + 32, +32) hold dS^T
       tmem_st32(tB + lane_off + half * 64, ppk);
