@@ -157,10 +157,23 @@ def cpu_tokens_per_s(seconds, sample, wl):
     return sample["S"] * (sample["H"] / wl["Hq"]) / seconds
 
 
+def use_host_cores():
+    """torch.distributed.run starts its workers with OMP_NUM_THREADS=1; the CPU arm is meant to use
+    the host's cores, so give torch as many threads as a plain start takes (one per physical core)."""
+    try:
+        n_aff = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n_aff = os.cpu_count() or 1
+    want = max(1, n_aff // 2)
+    if torch.get_num_threads() < want:
+        torch.set_num_threads(want)
+
+
 def run_reference(args, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    use_host_cores()
     for _ in range(args.warmup):
         cpu_pass(CPU_SAMPLE, wl["W"], wl["n_sink"], wl["seed"])
     times = [cpu_pass(CPU_SAMPLE, wl["W"], wl["n_sink"], wl["seed"]) for _ in range(args.steps)]
@@ -398,6 +411,7 @@ def main():
             line["e2e"] = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d * n,
                            "d2h_bytes_per_step": d2h * n, "ms_per_step": e2e_ms}
         if n == 1 and not args.no_cpu_baseline:
+            use_host_cores()
             t = [cpu_pass(CPU_SAMPLE, W, n_sink, wl["seed"])]          # first call warms torch up
             t0 = time.perf_counter()
             runs = []
