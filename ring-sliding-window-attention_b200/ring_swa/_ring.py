@@ -196,24 +196,33 @@ class RingAttn(torch.autograd.Function):
         works = _exchange(ops)
 
         dk4, dv4 = torch.empty_like(k4), torch.empty_like(v4)
+        # Gradients that later ranks return are added in float32 and rounded once.  When they all land
+        # on a suffix of the chunk (halo gradients; no sink token inside the chunk), only that suffix is
+        # kept in float32: the local K/V go to the kernels as two spans, the body writing its
+        # gradients straight into dk/dv, the tail into a small accumulator.
+        acc, acc0 = None, 0
         if recvs:
-            acc = torch.empty((2,) + tuple(k4.shape), dtype=torch.float32, device=k4.device)
-            local = K.KVSpan(k4, v4, plan.q_pos_start, dk=acc[0], dv=acc[1])
+            acc0 = min(off for off, _n, _g in recvs)
+            if any(off + n != S for off, n, _g in recvs) or acc0 <= 0:
+                acc0 = 0
+            acc = torch.empty((2, B, S - acc0) + tuple(k4.shape[2:]), dtype=torch.float32, device=k4.device)
+            local = [K.KVSpan(k4[:, acc0:], v4[:, acc0:], plan.q_pos_start + acc0, dk=acc[0], dv=acc[1])]
+            if acc0 > 0:
+                local.insert(0, K.KVSpan(k4[:, :acc0], v4[:, :acc0], plan.q_pos_start, dk=dk4[:, :acc0], dv=dv4[:, :acc0]))
         else:
-            acc = None
-            local = K.KVSpan(k4, v4, plan.q_pos_start, dk=dk4, dv=dv4)
+            local = [K.KVSpan(k4, v4, plan.q_pos_start, dk=dk4, dv=dv4)]
         # second call: dK/dV of the local span, and dQ over every span (the received ones without
         # gradient buffers, their gradients are already on the wire)
         seen = [K.KVSpan(s.k, s.v, s.pos_start) for s in remote]
         flags = _C.BWD_FINISH | (0 if remote else _C.BWD_INIT)
-        K.bwd(q4, seen + [local], out, lse, do4, dq4, workspace=ws, flags=flags, **args)
+        K.bwd(q4, seen + local, out, lse, do4, dq4, workspace=ws, flags=flags, **args)
         _wait(works)
         if acc is not None:
             for off, n, g in recvs:
-                K.halo_accumulate(acc[0][:, off:off + n], g[0])
-                K.halo_accumulate(acc[1][:, off:off + n], g[1])
-            K.cast_from_f32(dk4, acc[0])
-            K.cast_from_f32(dv4, acc[1])
+                K.halo_accumulate(acc[0][:, off - acc0:off - acc0 + n], g[0])
+                K.halo_accumulate(acc[1][:, off - acc0:off - acc0 + n], g[1])
+            K.cast_from_f32(dk4[:, acc0:], acc[0])
+            K.cast_from_f32(dv4[:, acc0:], acc[1])
         if varlen:
             dq4, dk4, dv4 = dq4.squeeze(0), dk4.squeeze(0), dv4.squeeze(0)
         return dq4, dk4, dv4, None, None, None, None, None, None
