@@ -203,7 +203,7 @@ class RingAttn(torch.autograd.Function):
         acc, acc0 = None, 0
         if recvs:
             acc0 = min(off for off, _n, _g in recvs)
-            if any(off + n != S for off, n, _g in recvs) or acc0 <= 0:
+            if any(off + n != S for off, n, _g in recvs) or acc0 <= 0 or len(remote) + 2 > _C.RSWA_MAX_SPANS:
                 acc0 = 0
             acc = torch.empty((2, B, S - acc0) + tuple(k4.shape[2:]), dtype=torch.float32, device=k4.device)
             local = [K.KVSpan(k4[:, acc0:], v4[:, acc0:], plan.q_pos_start + acc0, dk=acc[0], dv=acc[1])]
