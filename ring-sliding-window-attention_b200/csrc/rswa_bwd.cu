@@ -343,6 +343,11 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       uint32_t ppk[32];
 #pragma unroll
       for (int i = 0; i < 64; i += 2) ppk[i >> 1] = pack2<kBf16>(pr[i], pr[i + 1]);
+      // the delta row travels with the dO stage: it must have landed before it is read (the MMA
+      // warps wait for the stage before dP^T, the compute warps have not waited for anything of it yet)
+      ok = mbar_wait(&ctl->do_full[it & 1], (it >> 1) & 1, err, kErrWaitSoftmax);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       float npd[64];
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {

@@ -89,6 +89,27 @@ __device__ __forceinline__ void seq_of(const int* __restrict__ cu, int n_seqs, i
   end = (lo < n_seqs) ? __ldg(cu + lo + 1) : 0x7fffffff;
 }
 
+// Optional in-kernel timeline (development builds only, -DRSWA_TRACE): one chosen CTA stamps clock64()
+// into a per-file device array that a small extern "C" reader copies out.  Compiles to nothing otherwise.
+#ifdef RSWA_TRACE
+#ifndef RSWA_TRACE_CTA
+#define RSWA_TRACE_CTA 2000
+#endif
+#define RSWA_TRACE_SLOTS 2048
+#define RSWA_TRACE_DECL(name)                                                                    \
+  static __device__ long long g_trace_##name[RSWA_TRACE_SLOTS];                                  \
+  extern "C" int rswa_trace_read_##name(long long* out) {                                         \
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace_##name, sizeof(g_trace_##name)));  \
+  }
+#define RSWA_TRC(name, cond, slot)                                                               \
+  do {                                                                                           \
+    if (blockIdx.x == RSWA_TRACE_CTA && (cond) && (slot) < RSWA_TRACE_SLOTS) g_trace_##name[slot] = clock64(); \
+  } while (0)
+#else
+#define RSWA_TRACE_DECL(name)
+#define RSWA_TRC(name, cond, slot) do { } while (0)
+#endif
+
 // host side -------------------------------------------------------------------------------
 void set_error(const char* fmt, ...);
 // 4-D map over a [batch, tokens, heads, 128] 16-bit tensor (strides in elements), box = 64

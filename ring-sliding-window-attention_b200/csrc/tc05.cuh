@@ -11,10 +11,10 @@ namespace tc05 {
 // Upper bound on polls of any mbarrier wait.  A wait that runs out sets the error word and the
 // kernel drains and returns instead of hanging the device.
 #ifndef RSWA_SPIN_LIMIT
-#define RSWA_SPIN_LIMIT (1u << 24)
+#define RSWA_SPIN_LIMIT (1u << 28)
 #endif
 #ifndef RSWA_WAIT_LIMIT_NS
-#define RSWA_WAIT_LIMIT_NS 200000000ull /* 0.2 s per wait */
+#define RSWA_WAIT_LIMIT_NS 2000000000ull /* 2 s per wait */
 #endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -293,6 +293,12 @@ __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 // Two fp32 -> one 32-bit word holding two 16-bit floats, `lo` in bits 15..0.
 template <bool kBf16>

@@ -62,6 +62,60 @@ def check_device_status(device: Optional[torch.device] = None) -> None:
         raise RuntimeError(f"ring_swa kernel reported device-side error code {code} (a bounded wait ran out)")
 
 
+class _StatusMirror:
+    """Pinned host copy of a device's status word, refreshed asynchronously after a backward."""
+
+    def __init__(self, device: torch.device):
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+
+
+_mirrors = {}
+
+
+def _mirror(device: torch.device) -> _StatusMirror:
+    key = (device.type, device.index)
+    if key not in _mirrors:
+        _mirrors[key] = _StatusMirror(device)
+    return _mirrors[key]
+
+
+def mirror_status(device: torch.device) -> None:
+    """Enqueues a copy of the status word to pinned host memory behind the kernels launched so far.
+
+    The word is sticky on the device (kernels that start after it was raised do no work), so the
+    host has to learn of it without a synchronisation in the hot loop: the public functions call
+    this after every backward and raise_if_reported() at the start of the next call.  Skipped
+    inside a stream capture."""
+    if torch.cuda.is_current_stream_capturing():
+        return
+    m = _mirror(device)
+    m.host.copy_(status_word(device), non_blocking=True)
+    m.event.record()
+    m.pending = True
+
+
+def raise_if_reported(device: torch.device, wait: bool = False) -> None:
+    """Raises RuntimeError if the last mirrored status word was non-zero, and clears the word so that
+    the following call runs normally.  Without `wait` a copy still in flight is left for later."""
+    m = _mirrors.get((device.type, device.index))
+    if m is None or not m.pending or torch.cuda.is_current_stream_capturing():
+        return
+    if wait:
+        m.event.synchronize()
+    elif not m.event.query():
+        return
+    m.pending = False
+    code = int(m.host[0])
+    if code != 0:
+        m.host.zero_()
+        status_word(device).zero_()
+        raise RuntimeError(f"ring_swa: a kernel of an earlier call gave up on a bounded device-side wait "
+                           f"(code {code}); the results of that call are invalid. The status word has been "
+                           f"cleared, later calls run normally.")
+
+
 def _dtype_code(t: torch.Tensor) -> int:
     if t.dtype == torch.bfloat16:
         return _C.DTYPE_BF16

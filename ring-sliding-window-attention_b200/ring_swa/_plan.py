@@ -35,7 +35,10 @@ class HaloSend:
 
 @dataclass
 class SinkRecv:
-    owner: int        # group rank that holds the sink tokens
+    """One piece of the sink tokens: the part of them that one earlier rank holds.  The first n_sink
+    tokens of a sequence that starts fewer than n_sink tokens before a chunk boundary (or n_sink > S)
+    lie on several ranks, hence a list of pieces, one message each."""
+    owner: int        # group rank that holds these sink tokens
     pos_start: int    # their global position
     n: int
 
@@ -56,7 +59,7 @@ class RingPlan:
     n_sink: int
     halo_recv: List[HaloRecv] = field(default_factory=list)
     halo_send: List[HaloSend] = field(default_factory=list)
-    sink_recv: Optional[SinkRecv] = None
+    sink_recv: List[SinkRecv] = field(default_factory=list)   # ascending position, one per owning rank
     sink_send: List[SinkSend] = field(default_factory=list)
     # query tiles [halo_tile_end, n_tiles) see local keys only (and the sink)
     halo_tile_end: int = 0
@@ -79,7 +82,7 @@ def seq_start_of(pos: int, cu: Optional[Sequence[int]]) -> int:
     return int(cu[i])
 
 
-def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv], Optional[SinkRecv]]:
+def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv], List[SinkRecv]]:
     """What rank r must receive: (lowest needed window position, halos, sink).
 
     The sink tokens of the sequence that crosses the rank's left edge always travel as their own
@@ -90,13 +93,16 @@ def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv]
     left = r * S
     s_cross = seq_start_of(left, cu)
     lo = max(s_cross, left - W, 0)
-    sink = None
+    sink: List[SinkRecv] = []
     if n_sink > 0 and s_cross < left:
-        owner = s_cross // S
-        end = min(s_cross + n_sink, left, (owner + 1) * S)
-        if end > s_cross:
-            sink = SinkRecv(owner=owner, pos_start=s_cross, n=end - s_cross)
-            lo = max(lo, end)
+        end = min(s_cross + n_sink, left)
+        a = s_cross
+        while a < end:  # one piece per rank that owns some of [s_cross, end)
+            owner = a // S
+            b = min(end, (owner + 1) * S)
+            sink.append(SinkRecv(owner=owner, pos_start=a, n=b - a))
+            a = b
+        lo = max(lo, end)
     halos: List[HaloRecv] = []
     h = 1
     while r - h >= 0:
@@ -122,8 +128,9 @@ def make_plan(cp: int, rank: int, S: int, W: int, n_sink: int, cu: Optional[Sequ
         for hr in halos:
             if hr.src == rank:
                 plan.halo_send.append(HaloSend(hop=hr.hop, dst=r, length=hr.length))
-        if sink is not None and sink.owner == rank:
-            plan.sink_send.append(SinkSend(dst=r, offset=sink.pos_start - rank * S, n=sink.n))
+        for piece in sink:
+            if piece.owner == rank:
+                plan.sink_send.append(SinkSend(dst=r, offset=piece.pos_start - rank * S, n=piece.n))
     if plan.halo_recv:
         # local query a (position rank*S + a) reaches below the chunk iff a < W
         plan.halo_tile_end = min(plan.n_tiles, (min(W, S) + TILE - 1) // TILE)

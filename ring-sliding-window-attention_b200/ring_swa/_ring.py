@@ -80,13 +80,15 @@ class RingAttn(torch.autograd.Function):
     def forward(ctx, q, k, v, window: int, n_sink: int, softmax_scale: float,
                 cu_seqlens: Optional[torch.Tensor], cu_host: Optional[Sequence[int]], ring: RingCtx):
         varlen = cu_seqlens is not None
+        if q.is_cuda:
+            K.raise_if_reported(q.device)  # a time-out reported by an earlier call's kernels
         q4, k4, v4 = (_dense(x).unsqueeze(0) if varlen else _dense(x) for x in (q, k, v))
         if v4.stride() != k4.stride():
             v4 = v4.contiguous()
             k4 = k4.contiguous()
         B, S, Hq, D = q4.shape
         plan = make_plan(ring.cp, ring.rank, S, window, n_sink, cu_host)
-        if 1 + len(plan.halo_recv) + (plan.sink_recv is not None) > _C.RSWA_MAX_SPANS:
+        if 1 + len(plan.halo_recv) + len(plan.sink_recv) > _C.RSWA_MAX_SPANS:
             raise ValueError("window reaches over more ranks than one call supports "
                              f"({len(plan.halo_recv)} hops)")
         pos0 = plan.q_pos_start
@@ -94,16 +96,15 @@ class RingAttn(torch.autograd.Function):
 
         # -- post the exchanges
         sink_ops, halo_ops, keep = [], [], []
-        sink_span = None
+        sink_spans = []
         for s in plan.sink_send:
             buf = torch.stack([k4[:, s.offset:s.offset + s.n], v4[:, s.offset:s.offset + s.n]])
             keep.append(buf)
             sink_ops.append(dist.P2POp(dist.isend, buf, ring.global_rank(s.dst), ring.group))
-        if plan.sink_recv is not None:
-            sr = plan.sink_recv
+        for sr in plan.sink_recv:
             sbuf = torch.empty((2, B, sr.n) + tuple(k4.shape[2:]), dtype=k4.dtype, device=k4.device)
             sink_ops.append(dist.P2POp(dist.irecv, sbuf, ring.global_rank(sr.owner), ring.group))
-            sink_span = K.KVSpan(sbuf[0], sbuf[1], sr.pos_start)
+            sink_spans.append(K.KVSpan(sbuf[0], sbuf[1], sr.pos_start))
         packed = {}
         for s in plan.halo_send:
             if s.length not in packed:
@@ -122,14 +123,14 @@ class RingAttn(torch.autograd.Function):
         lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q4.device)
         args = dict(window=window, n_sink=n_sink, scale=softmax_scale, q_pos_start=pos0, cu_seqlens=cu_seqlens)
         _wait(sink_works)
-        near = ([sink_span] if sink_span is not None else []) + [local]
+        near = sink_spans + [local]
         if not halo_spans:
             K.fwd(q4, near, out=out, lse=lse, **args)
         elif window < S:
             nb = plan.halo_tile_end
             K.fwd(q4, near, out=out, lse=lse, q_tiles=(nb, plan.n_tiles), **args)
             _wait(halo_works)
-            spans = ([sink_span] if sink_span is not None else []) + halo_spans[::-1] + [local]
+            spans = sink_spans + halo_spans[::-1] + [local]
             K.fwd(q4, spans, out=out, lse=lse, q_tiles=(0, nb), **args)
         else:
             K.fwd(q4, near, out=out, lse=lse, **args)
@@ -140,9 +141,8 @@ class RingAttn(torch.autograd.Function):
 
         ctx.save_for_backward(q4, k4, v4, out, lse, cu_seqlens,
                               *[t for s in halo_spans for t in (s.k, s.v)],
-                              *([sink_span.k, sink_span.v] if sink_span is not None else []))
+                              *[t for s in sink_spans for t in (s.k, s.v)])
         ctx.plan, ctx.ring, ctx.args, ctx.varlen = plan, ring, args, varlen
-        ctx.keep_alive = keep + list(packed.values())
         return out.squeeze(0) if varlen else out
 
     @staticmethod
@@ -170,11 +170,13 @@ class RingAttn(torch.autograd.Function):
             g = grad_pair(hk.shape)
             remote.append(K.KVSpan(hk, hv, r.pos_start, dk=g[0], dv=g[1]))
             remote_grads.append(g)
-        sink_grad = None
-        if plan.sink_recv is not None:
+        sink_remote, sink_grads = [], []
+        for sr in plan.sink_recv:
             sk, sv = rest.pop(0), rest.pop(0)
-            sink_grad = grad_pair(sk.shape)
-            remote.insert(0, K.KVSpan(sk, sv, plan.sink_recv.pos_start, dk=sink_grad[0], dv=sink_grad[1]))
+            g = grad_pair(sk.shape)
+            sink_remote.append(K.KVSpan(sk, sv, sr.pos_start, dk=g[0], dv=g[1]))
+            sink_grads.append(g)
+        remote = sink_remote + remote
 
         dq4 = torch.empty_like(q4)
         ws = K.bwd_workspace(q4)
@@ -183,8 +185,8 @@ class RingAttn(torch.autograd.Function):
             K.bwd(q4, remote, out, lse, do4, dq4, workspace=ws, flags=_C.BWD_INIT, **args)
             for r, g in zip(plan.halo_recv, remote_grads):
                 ops.append(dist.P2POp(dist.isend, g, ring.global_rank(r.src), ring.group))
-            if sink_grad is not None:
-                ops.append(dist.P2POp(dist.isend, sink_grad, ring.global_rank(plan.sink_recv.owner), ring.group))
+            for sr, g in zip(plan.sink_recv, sink_grads):
+                ops.append(dist.P2POp(dist.isend, g, ring.global_rank(sr.owner), ring.group))
         for s in plan.halo_send:
             g = grad_pair((B, s.length) + tuple(k4.shape[2:]))
             ops.append(dist.P2POp(dist.irecv, g, ring.global_rank(s.dst), ring.group))
@@ -223,6 +225,8 @@ class RingAttn(torch.autograd.Function):
                 K.halo_accumulate(acc[1][:, off - acc0:off - acc0 + n], g[1])
             K.cast_from_f32(dk4[:, acc0:], acc[0])
             K.cast_from_f32(dv4[:, acc0:], acc[1])
+        if q4.is_cuda:
+            K.mirror_status(q4.device)
         if varlen:
             dq4, dk4, dv4 = dq4.squeeze(0), dk4.squeeze(0), dv4.squeeze(0)
         return dq4, dk4, dv4, None, None, None, None, None, None

@@ -14,6 +14,10 @@ def _varlen_prologue(q, k, v, cu_seqlens, cp_size):
     # one device-to-host copy, where the reference has its own (and several more further down):
     # the global cumulative lengths drive the halo plan on the host
     cu_host = [int(x) for x in cu_seqlens.tolist()]
+    if q.is_cuda:
+        # the copy above has synchronised with the device anyway: a good moment to look at the status word
+        from .. import _kernels
+        _kernels.raise_if_reported(q.device, wait=True)
     # ring_swa/sliding_window/varlen.py:401-403; evaluated before cp_group is looked at, so a
     # missing cp_size raises TypeError there as well
     assert q.shape[0] == cu_host[-1] // cp_size, "cu_seqlens does not match with sequence length per rank"

@@ -116,6 +116,9 @@ def test_fp16_and_fp32_grads_and_strided_inputs():
     (2, 192, 90, 0, [100, 1, 155, 128]),
     (4, 128, 140, 1, [290, 222]),
     (4, 128, 50, 2, [130, 200, 182]),
+    (4, 128, 40, 3, [127, 128, 257]),    # sink tokens of a sequence lie on two ranks (127 | 128, 129)
+    (3, 200, 30, 5, [398, 202]),         # ... 398, 399 on rank 1 and 400-402 on rank 2, needed by nobody later
+    (4, 128, 20, 4, [254, 258]),         # sinks 254, 255 | 256, 257: rank 3 needs both pieces
 ])
 def test_spans_emulated_ranks(cp, S, W, n_sink, lens):
     """Every rank's forward/backward over (sink | halo... | local) spans, run one after the other on
@@ -139,9 +142,8 @@ def test_spans_emulated_ranks(cp, S, W, n_sink, lens):
         plan = make_plan(cp, r, S, W, n_sink, cu)
         sl = slice(r * S, (r + 1) * S)
         spans, ranges = [], []
-        if plan.sink_recv is not None:
-            a, n = plan.sink_recv.pos_start, plan.sink_recv.n
-            ranges.append((a, a + n))
+        for sr in plan.sink_recv:
+            ranges.append((sr.pos_start, sr.pos_start + sr.n))
         for h in plan.halo_recv[::-1]:
             ranges.append((h.pos_start, h.pos_start + h.length))
         ranges.append((r * S, (r + 1) * S))

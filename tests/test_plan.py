@@ -21,7 +21,7 @@ def test_nonvarlen_halo_matches_reference_round_count(cp, S, W):
         for h in p.halo_recv:
             assert h.pos_start + h.length == pos and h.src == r - h.hop
             pos = h.pos_start
-        assert p.sink_recv is None and not p.sink_send
+        assert not p.sink_recv and not p.sink_send
 
 
 def test_sends_mirror_receives():
@@ -32,10 +32,10 @@ def test_sends_mirror_receives():
                 for r, p in enumerate(plans):
                     for h in p.halo_recv:
                         assert any(s.dst == r and s.length == h.length for s in plans[h.src].halo_send)
-                    if p.sink_recv is not None:
-                        o = p.sink_recv.owner
-                        assert any(s.dst == r and s.n == p.sink_recv.n and
-                                   s.offset + o * 16 == p.sink_recv.pos_start for s in plans[o].sink_send)
+                    for piece in p.sink_recv:
+                        o = piece.owner
+                        assert any(s.dst == r and s.n == piece.n and
+                                   s.offset + o * 16 == piece.pos_start for s in plans[o].sink_send)
                     n_recv = sum(1 for q in plans for h in q.halo_recv if h.src == r)
                     assert n_recv == len(p.halo_send)
 
@@ -49,22 +49,85 @@ def test_varlen_halo_stops_at_sequence_start():
 
 
 def test_sink_travels_separately_and_never_overlaps_the_halo():
+    def only(plan):
+        assert len(plan.sink_recv) == 1
+        return plan.sink_recv[0]
     p = make_plan(4, 3, 16, 5, 1, None)
-    assert (p.sink_recv.owner, p.sink_recv.pos_start, p.sink_recv.n) == (0, 0, 1)
+    assert (only(p).owner, only(p).pos_start, only(p).n) == (0, 0, 1)
     # window reaches token 0: the sink still has its own message and the halo starts behind it
     p = make_plan(4, 1, 16, 20, 1, None)
-    assert (p.sink_recv.pos_start, p.sink_recv.n) == (0, 1)
+    assert (only(p).pos_start, only(p).n) == (0, 1)
     assert [(h.pos_start, h.length) for h in p.halo_recv] == [(1, 15)]
     p = make_plan(4, 1, 16, 14, 4, None)
-    assert (p.sink_recv.pos_start, p.sink_recv.n) == (0, 4)
+    assert (only(p).pos_start, only(p).n) == (0, 4)
     assert [(h.pos_start, h.length) for h in p.halo_recv] == [(4, 12)]
     # the sequence starts on this rank: its sink is local, nothing extra travels
-    assert make_plan(4, 2, 16, 5, 1, [0, 32, 64]).sink_recv is None
-    assert make_plan(4, 0, 16, 5, 1, None).sink_recv is None
+    assert make_plan(4, 2, 16, 5, 1, [0, 32, 64]).sink_recv == []
+    assert make_plan(4, 0, 16, 5, 1, None).sink_recv == []
     # packed: the crossing sequence starts inside the window's reach on the previous rank
     p = make_plan(2, 1, 300, 50, 1, [0, 280, 600])
-    assert (p.sink_recv.owner, p.sink_recv.pos_start, p.sink_recv.n) == (0, 280, 1)
+    assert (only(p).owner, only(p).pos_start, only(p).n) == (0, 280, 1)
     assert [(h.pos_start, h.length) for h in p.halo_recv] == [(281, 19)]
+
+
+def test_sink_tokens_that_straddle_a_chunk_boundary_travel_in_pieces():
+    # cp=3, S=6, W=3, two sink tokens, the last sequence starts at 5: its sinks are tokens 5 (rank 0) and
+    # 6 (rank 1); rank 2 needs both and neither is inside its window
+    p = make_plan(3, 2, 6, 3, 2, [0, 1, 3, 5, 18])
+    assert [(s.owner, s.pos_start, s.n) for s in p.sink_recv] == [(0, 5, 1), (1, 6, 1)]
+    assert [(h.pos_start, h.length) for h in p.halo_recv] == [(9, 3)]
+    assert [(s.dst, s.offset, s.n) for s in make_plan(3, 0, 6, 3, 2, [0, 1, 3, 5, 18]).sink_send] == [(1, 5, 1), (2, 5, 1)]
+    assert [(s.dst, s.offset, s.n) for s in make_plan(3, 1, 6, 3, 2, [0, 1, 3, 5, 18]).sink_send] == [(2, 0, 1)]
+    # more sink tokens than a chunk holds
+    p = make_plan(4, 3, 4, 2, 9, None)
+    assert [(s.owner, s.pos_start, s.n) for s in p.sink_recv] == [(0, 0, 4), (1, 4, 4), (2, 8, 1)]
+    assert [(h.pos_start, h.length) for h in p.halo_recv] == [(10, 2)]
+
+
+def _visible_keys(p, cu, W, n_sink):
+    """Keys query position p sees, from the mask definition."""
+    if cu is None:
+        s = 0
+    else:
+        s = max(c for c in cu if c <= p)
+    return {t for t in range(s, p + 1) if p - t <= W or t < s + n_sink}
+
+
+def test_plan_covers_every_visible_key_exactly_once():
+    """Brute force over random geometries: local chunk + halos + sink pieces hold every key any local
+    query sees, no position twice, and the tiles declared halo-free really need no halo."""
+    import random
+    rng = random.Random(7)
+    for trial in range(1500):
+        cp = rng.randint(1, 5)
+        S = rng.choice([1, 2, 3, 6, 8, 16])
+        W = rng.randint(0, 3 * S + 2)
+        n_sink = rng.choice([0, 1, 2, 3, 5])
+        T = cp * S
+        if rng.random() < 0.5:
+            cu = None
+        else:
+            cuts = sorted(rng.sample(range(1, T), min(T - 1, rng.randint(0, 4)))) if T > 1 else []
+            cu = [0] + cuts + [T]
+        for r in range(cp):
+            plan = make_plan(cp, r, S, W, n_sink, cu)
+            have = list(range(r * S, (r + 1) * S))
+            for h in plan.halo_recv:
+                assert h.src == r - h.hop and (r - h.hop) * S <= h.pos_start and h.pos_start + h.length == (r - h.hop + 1) * S
+                have += range(h.pos_start, h.pos_start + h.length)
+            for sr in plan.sink_recv:
+                assert sr.owner * S <= sr.pos_start and sr.pos_start + sr.n <= (sr.owner + 1) * S
+                have += range(sr.pos_start, sr.pos_start + sr.n)
+            assert len(have) == len(set(have)), (cp, r, S, W, n_sink, cu)
+            need = set()
+            for p in range(r * S, (r + 1) * S):
+                need |= _visible_keys(p, cu, W, n_sink)
+            assert need <= set(have), (cp, r, S, W, n_sink, cu, sorted(need - set(have)))
+            near = set(range(r * S, (r + 1) * S))
+            for sr in plan.sink_recv:
+                near |= set(range(sr.pos_start, sr.pos_start + sr.n))
+            for p in range(r * S + plan.halo_tile_end * 128, (r + 1) * S):
+                assert _visible_keys(p, cu, W, n_sink) <= near
 
 
 def test_rejects_bad_geometry():

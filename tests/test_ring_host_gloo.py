@@ -85,3 +85,16 @@ def test_ring_matches_dense_oracle_cp2():
     ]
     res = _spawn(2, 29741, jobs)
     _assert_small(res, jobs, TOL)
+
+
+@pytest.mark.timeout(600)
+def test_sink_tokens_on_two_ranks_cp3():
+    """The first tokens of a sequence that starts just before a chunk boundary lie on two ranks; a
+    later rank gets them as two pieces and returns their gradients to both owners."""
+    jobs = [
+        _dense_job("ring_streaming_llm_attn_varlen", 600, None, 2, 1, 8, 40, 31, cu=[0, 199, 600], n_sink=3),
+        _dense_job("ring_streaming_llm_attn_varlen", 600, None, 2, 2, 8, 70, 32, cu=[0, 50, 398, 600], n_sink=5),
+        _dense_job("ring_streaming_llm_attn", 12, 1, 2, 1, 8, 2, 33, n_sink=9),   # more sink tokens than a chunk holds
+    ]
+    res = _spawn(3, 29751, jobs)
+    _assert_small(res, jobs, TOL)
