@@ -1,25 +1,30 @@
 // Forward kernel: banded (sliding-window + sink) softmax attention on the sm_100a tensor cores.
 //
-// One CTA owns two consecutive 128-row query tiles of one head and walks the key tiles either of
-// them can see.  Two softmax warp groups (one per query tile) work in ping-pong against ONE
-// MMA-issuing warp that serves the two query tiles strictly in turn, so that the tensor cores
+// A work item is a block of two consecutive 128-row query tiles of one head; it walks the key tiles
+// either of them can see.  Two softmax warp groups (one per query tile) work in ping-pong against
+// ONE MMA-issuing thread that serves the two query tiles strictly in turn, so that the tensor cores
 // compute one tile's products while the other tile's exponentials run:
 //
 //   S_w = Q_w K^T      tcgen05.mma, both operands in shared memory (K-major), accumulator in TMEM
 //   P_w = softmax      warp group w: one query row per thread, whole S row in registers, P written
-//                      back (16-bit) over the same TMEM columns
+//                      back (16-bit) over the same TMEM columns, in two halves of 64 keys
 //   O_w += P_w V       tcgen05.mma, A = P_w from TMEM, B = V from shared memory (MN-major)
 //
-// The issue order is  O_0 += P_0 V(j), S_0 = Q_0 K(j+1)^T, O_1 += P_1 V(j), S_1 = Q_1 K(j+1)^T, ...:
+// The issue order is  O_0 += P_0 V(g), S_0 = Q_0 K(g+1)^T, O_1 += P_1 V(g), S_1 = Q_1 K(g+1)^T, ...:
 // S_w of the NEXT key tile goes right behind O_w += P_w V of the current one (tcgen05.mma
 // instructions of one thread execute in issue order, so the overwrite of P_w's columns cannot
 // overtake its last reader), and because everything comes from one thread the two tiles' products
 // never interleave: S_0 becomes ready one product pair ahead of S_1, which keeps the two softmax
 // groups half a period apart (with one issuing warp per tile the products of both tiles interleave
 // on the tensor pipe, both S become ready together and the two groups run their exponentials at
-// the same time, then both wait).  Loads travel in units of {K(j+1), V(j)}, the two tiles iteration
-// j reads, through a two-stage ring.  The finished
-// rows leave through shared memory so that every store instruction writes whole rows.
+// the same time, then both wait).
+//
+// The kernel is persistent: one CTA per SM strides over the items, and every pipeline keeps running
+// across item boundaries.  Loads travel as a stream of units {K of the next key tile, V of the
+// current one} -- the two tiles one step of the MMA loop reads -- through a two-stage ring; at an
+// item boundary the unit simply carries the next item's first K tile, so S of the next item is
+// computed while the softmax groups still normalise and store the rows of the finished one (staged
+// through shared memory so that every store instruction writes whole row segments).
 // TMEM: [0,128) S_0/P_0, [128,256) S_1/P_1, [256,384) O_0, [384,512) O_1.
 //
 // Key tiles that no row of the block can see are never loaded (rswa_tiles.cuh); a query tile skips
@@ -40,60 +45,73 @@ namespace {
 
 constexpr int kFwdThreads = 384;   // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-7 / 8-11 softmax
 constexpr int kFwdTmemCols = 512;
-constexpr int kFwdSmemTiles = 7 * kTileBytes;  // Q_0, Q_1, K(0), 2 x {K(j+1), V(j)}
+constexpr int kFwdSmemTiles = 7 * kTileBytes;  // Q_0, Q_1, output staging (one tile), 2 units of {K, V}
 constexpr int kUnits = 2;
+constexpr int kSoftmaxWarps = 8;
+#ifndef RSWA_FWD_POLY_EVERY
+#define RSWA_FWD_POLY_EVERY 4
+#endif
+constexpr int kPolyEvery = RSWA_FWD_POLY_EVERY;  // 0: every exponential on the special-function unit
+
+// flags of a unit, written by the producer ahead of the unit's loads
+enum : uint32_t {
+  kActMask = 3u,     // bit w: the unit's K tile matters to query tile w
+  kFirst = 4u,       // the K tile is the first of its item (the products use a new Q, O starts over)
+  kLast = 8u,        // ... the last of its item (Q may be replaced once its S products are done)
+  kHasK = 16u,       // the unit carries a K tile
+  kHasV = 32u,       // the unit carries the V tile of the previous unit's K tile
+  kStop = 64u,       // nothing follows
+};
 
 struct FwdCtl {
-  uint64_t q_full, k0_full, kv_full[kUnits], kv_free[kUnits], s_ready[2], p_ready[2][2], pv_done[2];
+  uint64_t q_full, q_free, kv_full[kUnits], kv_free[kUnits];
+  uint64_t s_ready[2], p_ready[2][2], pv_done[2], o_free[2];
+  uint64_t geom_full[2], geom_free[2];
   uint32_t tmem_base;
   int err;
-  // which of the two query tiles need key tile j (bit w), written by the producer ahead of the load
-  // that carries the tile's K and read by the MMA-issuing thread behind its wait for that load; two
-  // units are in flight at most, so 8 slots are never overwritten while still unread
-  uint32_t tile_flags[8];
-  QBlockGeom geom;
+  // two units are in flight at most, so 8 slots are never overwritten while still unread
+  uint32_t unit_flags[8];
+  int item[2];  // work item of each geometry slot, -1: no more work
+  QBlockGeom geom[2];
 };
 
 constexpr int kFwdSmemBytes = kFwdSmemTiles + 1024;
 static_assert(sizeof(FwdCtl) <= 1024, "control block too large");
 static_assert(kFwdSmemBytes <= 232448, "shared memory budget");
 
-// visible(p, t) for the row owning (lo, hi, seq, sink_end): t in [lo, hi] or a sink position <= hi
-__device__ __forceinline__ bool key_visible(int t, int lo, int hi, int seq, int sink_end, int span_end) {
-  return t <= hi && t < span_end && (t >= lo || (t >= seq && t < sink_end));
+struct FwdItem {
+  int blk, h, b, hk, tile0;
+};
+__device__ __forceinline__ FwdItem fwd_item(const FwdKernelParams& p, int n_blocks, int it) {
+  FwdItem d;  // query block fastest (late blocks, which see the most keys, first), then head, then batch row
+  d.blk = n_blocks - 1 - it % n_blocks;
+  it /= n_blocks;
+  d.h = it % p.hq;
+  d.b = it / p.hq;
+  d.hk = d.h / (p.hq / p.hkv);
+  d.tile0 = p.q_tile_begin + 2 * d.blk;
+  return d;
 }
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
-rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
+rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p, int n_blocks, int n_items) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* sQ = smem;                     // two query tiles
-  uint8_t* sK0 = smem + 2 * kTileBytes;   // K of the first key tile
-  uint8_t* sU = smem + 3 * kTileBytes;    // two units, each K(j+1) then V(j)
+  uint8_t* sQ = smem;                       // two query tiles
+  uint8_t* sStage = smem + 2 * kTileBytes;  // output staging: 16 KB per softmax group
+  uint8_t* sU = smem + 3 * kTileBytes;      // two units, each a K tile then a V tile
   FwdCtl* ctl = reinterpret_cast<FwdCtl*>(smem + kFwdSmemTiles);
-  QBlockGeom* geom = &ctl->geom;
 
   RSWA_TRC(fwd, threadIdx.x == 0, 1920);
   // a device-side error was already reported on this stream: do not pile further time-outs on it
   if (__syncthreads_or(*reinterpret_cast<volatile int*>(p.status) != 0)) return;
-  RSWA_TRC(fwd, threadIdx.x == 0, 1921);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // work item: query block fastest, then head, then batch row
-  const int n_blocks = (p.n_q_tiles + 1) >> 1;
-  int idx = blockIdx.x;
-  const int blk = idx % n_blocks;
-  idx /= n_blocks;
-  const int h = idx % p.hq;
-  const int b = idx / p.hq;
-  const int hk = h / (p.hq / p.hkv);
-  const int tile0 = p.q_tile_begin + 2 * blk;
-
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
-    mbar_init(&ctl->k0_full, 1);
+    mbar_init(&ctl->q_free, 1);
     for (int i = 0; i < kUnits; ++i) {
       mbar_init(&ctl->kv_full[i], 1);
       mbar_init(&ctl->kv_free[i], 1);
@@ -103,11 +121,12 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
       mbar_init(&ctl->p_ready[i][0], 4);  // one arrival per softmax warp and half of P
       mbar_init(&ctl->p_ready[i][1], 4);
       mbar_init(&ctl->pv_done[i], 1);
+      mbar_init(&ctl->o_free[i], 4);
+      mbar_init(&ctl->geom_full[i], 1);
+      mbar_init(&ctl->geom_free[i], kSoftmaxWarps);
     }
     ctl->err = (smem_u32(smem) & 1023u) ? 199 : 0;
     mbar_fence_init();
-    qblock_geometry<kTile>(geom, p.cu, p.n_seqs, p.n_spans, p.span_pos, p.span_len, p.q_pos_start, p.q_len,
-                           p.window, p.n_sink, tile0, p.q_tile_begin + p.n_q_tiles);
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, kFwdTmemCols);
@@ -119,110 +138,153 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
 
   const uint32_t tmem = ctl->tmem_base;
   volatile int* err = &ctl->err;
-  const int n_tiles = (ctl->err != 0) ? 0 : geom->n_tiles;
+  const int n_work = (ctl->err != 0) ? 0 : n_items;
   RSWA_TRC(fwd, threadIdx.x == 0, 1922);
 
   if (warp < 4) {
     setmaxnreg_dec<88>();
-    if (warp == 0 && lane == 0 && n_tiles > 0) {
-      // ------------------------------------------------------------------ TMA producer
-      // Loads travel in the order they are consumed: Q, K(0), then one unit per key tile j holding
-      // K(j+1) and V(j) -- the two tiles iteration j of the MMA loop reads, so that one barrier fills
-      // and one frees them.
-      const bool two = geom->n_valid[1] > 0;
-      mbar_expect_tx(&ctl->q_full, two ? 2 * kTileBytes : kTileBytes);
-      tma_load_4d(sQ, &p.q_map, &ctl->q_full, 0, h, tile0 * kTile, b);
-      tma_load_4d(sQ + kBoxBytes, &p.q_map, &ctl->q_full, 64, h, tile0 * kTile, b);
-      if (two) {
-        tma_load_4d(sQ + kTileBytes, &p.q_map, &ctl->q_full, 0, h, (tile0 + 1) * kTile, b);
-        tma_load_4d(sQ + kTileBytes + kBoxBytes, &p.q_map, &ctl->q_full, 64, h, (tile0 + 1) * kTile, b);
-      }
-      TileCursor c, cn;
-      cursor_begin<kTile>(geom, p.span_pos, p.span_len, c);
-      ctl->tile_flags[0] = (tile_active(geom, 0, c, p.n_sink) ? 1u : 0u) | (tile_active(geom, 1, c, p.n_sink) ? 2u : 0u);
-      mbar_expect_tx(&ctl->k0_full, kTileBytes);  // (release: the flags are visible to whoever sees the tile)
-      tma_load_4d(sK0, &p.k_map[c.span], &ctl->k0_full, 0, hk, c.tok, b);
-      tma_load_4d(sK0 + kBoxBytes, &p.k_map[c.span], &ctl->k0_full, 64, hk, c.tok, b);
+    if (warp == 0 && lane == 0) {
+      // ------------------------------------------------------------------ geometry + TMA producer
+      // Walks the items of this CTA, prepares each item's key-tile list one item ahead (two-slot
+      // ring) and streams the units.  Unit u carries the K tile of step u and the V tile of step
+      // u - 1; the V tile of an item's last key tile travels with the next item's first K tile, or
+      // alone when the next item has no key tile (or does not exist).
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j & 1;
-        const bool more = j + 1 < n_tiles;
-        uint8_t* unit = sU + st * 2 * kTileBytes;
-        cn = c;
-        cursor_next<kTile>(geom, p.span_pos, p.span_len, cn, more);
-        if (j >= kUnits) ok = mbar_wait<100>(&ctl->kv_free[st], ((j >> 1) - 1) & 1, err, kErrWaitProducer);
+      int u = 0, ic = 0;  // units issued, items with work so far
+      bool pend = false;  // a V tile still to be sent
+      int pv_span = 0, pv_tok = 0, pv_hk = 0, pv_b = 0;
+      auto unit_begin = [&](uint32_t flags, uint32_t bytes) -> bool {
+        const int st = u & 1;
+        if (u >= kUnits && !mbar_wait<100>(&ctl->kv_free[st], ((u >> 1) - 1) & 1, err, kErrWaitProducer)) return false;
+        ctl->unit_flags[u & 7] = flags;
+        if (bytes > 0) mbar_expect_tx(&ctl->kv_full[st], bytes);  // (release: the flags are visible to whoever sees the unit)
+        else mbar_arrive(&ctl->kv_full[st]);
+        return true;
+      };
+      auto load_v = [&]() {
+        uint8_t* dst = sU + (u & 1) * 2 * kTileBytes + kTileBytes;
+        tma_load_4d(dst, &p.v_map[pv_span], &ctl->kv_full[u & 1], 0, pv_hk, pv_tok, pv_b);
+        tma_load_4d(dst + kBoxBytes, &p.v_map[pv_span], &ctl->kv_full[u & 1], 64, pv_hk, pv_tok, pv_b);
+      };
+      for (int n = 0; ok; ++n) {
+        const int slot = n & 1;
+        if (n >= 2) ok = mbar_wait<100>(&ctl->geom_free[slot], ((n >> 1) - 1) & 1, err, kErrWaitProducer);
         if (!ok) break;
-        RSWA_TRC(fwd, j < 32, j * 32 + 16);
-        if (more)
-          ctl->tile_flags[(j + 1) & 7] =
-              (tile_active(geom, 0, cn, p.n_sink) ? 1u : 0u) | (tile_active(geom, 1, cn, p.n_sink) ? 2u : 0u);
-        mbar_expect_tx(&ctl->kv_full[st], more ? 2 * kTileBytes : kTileBytes);
-        if (more) {
-          tma_load_4d(unit, &p.k_map[cn.span], &ctl->kv_full[st], 0, hk, cn.tok, b);
-          tma_load_4d(unit + kBoxBytes, &p.k_map[cn.span], &ctl->kv_full[st], 64, hk, cn.tok, b);
+        const int it = static_cast<int>(blockIdx.x) + n * static_cast<int>(gridDim.x);
+        if (it >= n_work) {  // tell the softmax warps that the work has run out
+          ctl->item[slot] = -1;
+          mbar_arrive(&ctl->geom_full[slot]);
+          break;
         }
-        tma_load_4d(unit + kTileBytes, &p.v_map[c.span], &ctl->kv_full[st], 0, hk, c.tok, b);
-        tma_load_4d(unit + kTileBytes + kBoxBytes, &p.v_map[c.span], &ctl->kv_full[st], 64, hk, c.tok, b);
-        c = cn;
+        const FwdItem w = fwd_item(p, n_blocks, it);
+        QBlockGeom* geom = &ctl->geom[slot];
+        qblock_geometry<kTile>(geom, p.cu, p.n_seqs, p.n_spans, p.span_pos, p.span_len, p.q_pos_start, p.q_len,
+                               p.window, p.n_sink, w.tile0, p.q_tile_begin + p.n_q_tiles);
+        ctl->item[slot] = it;
+        mbar_arrive(&ctl->geom_full[slot]);
+        const int n_tiles = geom->n_tiles;
+        if (n_tiles == 0) {
+          if (pend) {  // the finished item's last V tile must not wait for an item that may never come
+            ok = unit_begin(kHasV, kTileBytes);
+            if (!ok) break;
+            load_v();
+            ++u;
+            pend = false;
+          }
+          continue;
+        }
+        TileCursor c;
+        cursor_begin<kTile>(geom, p.span_pos, p.span_len, c);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          const uint32_t flags = (tile_active(geom, 0, c, p.n_sink) ? 1u : 0u) | (tile_active(geom, 1, c, p.n_sink) ? 2u : 0u) |
+                                 (j == 0 ? kFirst : 0u) | (j + 1 == n_tiles ? kLast : 0u) | kHasK | (pend ? kHasV : 0u);
+          ok = unit_begin(flags, pend ? 2 * kTileBytes : kTileBytes);
+          if (!ok) break;
+          RSWA_TRC(fwd, n == 1 && j < 32, j * 32 + 16);
+          uint8_t* dst = sU + (u & 1) * 2 * kTileBytes;
+          tma_load_4d(dst, &p.k_map[c.span], &ctl->kv_full[u & 1], 0, w.hk, c.tok, w.b);
+          tma_load_4d(dst + kBoxBytes, &p.k_map[c.span], &ctl->kv_full[u & 1], 64, w.hk, c.tok, w.b);
+          if (pend) load_v();
+          ++u;
+          pend = true;
+          pv_span = c.span, pv_tok = c.tok, pv_hk = w.hk, pv_b = w.b;
+          if (j == 0) {
+            // Q of this item, once the last S product of the previous item has read the old one
+            if (ic > 0) ok = mbar_wait<100>(&ctl->q_free, (ic - 1) & 1, err, kErrWaitProducer);
+            if (!ok) break;
+            const bool two = geom->n_valid[1] > 0;
+            mbar_expect_tx(&ctl->q_full, two ? 2 * kTileBytes : kTileBytes);
+            tma_load_4d(sQ, &p.q_map, &ctl->q_full, 0, w.h, w.tile0 * kTile, w.b);
+            tma_load_4d(sQ + kBoxBytes, &p.q_map, &ctl->q_full, 64, w.h, w.tile0 * kTile, w.b);
+            if (two) {
+              tma_load_4d(sQ + kTileBytes, &p.q_map, &ctl->q_full, 0, w.h, (w.tile0 + 1) * kTile, w.b);
+              tma_load_4d(sQ + kTileBytes + kBoxBytes, &p.q_map, &ctl->q_full, 64, w.h, (w.tile0 + 1) * kTile, w.b);
+            }
+          }
+          cursor_next<kTile>(geom, p.span_pos, p.span_len, c, j + 1 < n_tiles);
+        }
+        ++ic;
       }
-    } else if (warp == 1 && n_tiles > 0) {
+      if (ok && pend) {
+        ok = unit_begin(kHasV, kTileBytes);
+        if (ok) {
+          load_v();
+          ++u;
+        }
+      }
+      if (ok) {
+        if (unit_begin(kStop, 0)) ++u;
+      }
+    } else if (warp == 1) {
       // ------------------------------------------------------------------ MMA issuer
       // ONE elected thread issues every product, the two query tiles strictly in turn, and does all the
       // waiting for them.  Its own instruction stream is the longest serial chain of the CTA (a lone
       // warp next to eight arithmetic-heavy ones gets an instruction through every 6-8 cycles), so it
-      // does as little as possible: no geometry (which tiles matter to which query tile comes from the
-      // producer's flags), one barrier per unit of loads, no warp votes.
-      if (elect_one()) {
+      // does as little as possible: no geometry (what a unit holds and which query tile it matters to
+      // comes from the producer's flags), one barrier per unit of loads, no warp votes.
+      if (elect_one() && n_work > 0) {
         constexpr uint32_t idesc_qk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
         constexpr uint32_t idesc_pv = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
         // descriptors are built once; per stage / k-step only their address field moves (16-byte units)
         constexpr uint32_t kTile16 = kTileBytes >> 4;
         const uint64_t dQ = smem_desc_sw128(smem_u32(sQ), 16, 1024);
-        const uint64_t dK0 = smem_desc_sw128(smem_u32(sK0), 16, 1024);
         const uint64_t dKu = smem_desc_sw128(smem_u32(sU), 16, 1024);
         const uint64_t dVu = smem_desc_sw128(smem_u32(sU) + kTileBytes, kBoxBytes, 1024);
         uint32_t pv_phase = 0;  // bit w: parity of p_ready[w][*] to wait for
-        uint32_t pv_any = 0;    // bit w: O_w holds a product already (accumulate)
-        bool ok = mbar_wait<0>(&ctl->q_full, 0, err, kErrWaitMma);
-        if (ok) ok = mbar_wait<0>(&ctl->k0_full, 0, err, kErrWaitMma);
-        uint32_t f_cur = 0;
-        if (ok) {
-          f_cur = ctl->tile_flags[0];
-          tc_fence_after();
-#pragma unroll
-          for (int w = 0; w < 2; ++w) {
-            if ((f_cur >> w) & 1u) {
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-                mma_ss(tmem + 128 * w, dQ + w * kTile16 + off, dK0 + off, idesc_qk, k > 0 ? 1u : 0u);
-              }
-              mma_commit(&ctl->s_ready[w]);
-            }
-          }
-        }
-        uint32_t kv_par = 0;  // parity of kv_full[j & 1] to wait for
-        for (int j = 0; j < n_tiles && ok; ++j) {
-          const bool more = j + 1 < n_tiles;
-          const int st = j & 1;
-          RSWA_TRC(fwd, j < 32, j * 32 + 24);
+        uint32_t pv_any = 0;    // bit w: O_w holds a product of the current item already (accumulate)
+        uint32_t of_cnt0 = 0, of_cnt1 = 0;  // items that have used O_w so far (phase of o_free[w])
+        uint32_t q_par = 0, kv_par = 0;
+        uint32_t f_prev = 0;    // flags of the unit whose K tile awaits its P V products
+        bool ok = true;
+        for (int u = 0; ok; ++u) {
+          const int st = u & 1;
+          RSWA_TRC(fwd, u >= 12 && u < 44, (u - 12) * 32 + 24);
           ok = mbar_wait<0>(&ctl->kv_full[st], kv_par, err, kErrWaitMma);
           if (!ok) break;
-          const uint32_t f_nxt = more ? ctl->tile_flags[(j + 1) & 7] : 0u;
-          RSWA_TRC(fwd, j < 32, j * 32 + 0);
+          const uint32_t f = ctl->unit_flags[u & 7];
+          if (f & kStop) break;
+          RSWA_TRC(fwd, u >= 12 && u < 44, (u - 12) * 32 + 0);
+          bool need_q = (f & kFirst) != 0;  // the S products below are the first to read a new Q
+          tc_fence_after();
           const uint64_t dKs = dKu + st * (2 * kTile16);
           const uint64_t dVs = dVu + st * (2 * kTile16);
 #pragma unroll
           for (int w = 0; w < 2; ++w) {
             const uint32_t tSw = tmem + 128 * w, tOw = tmem + 256 + 128 * w;
-            if ((f_cur >> w) & 1u) {
+            if ((f & kHasV) && ((f_prev >> w) & 1u)) {
+              if (!((pv_any >> w) & 1u)) {
+                // first product of an item into O_w: the previous item's rows must have been read out
+                const uint32_t cnt = w == 0 ? of_cnt0 : of_cnt1;
+                if (cnt > 0) ok = mbar_wait<0>(&ctl->o_free[w], (cnt - 1) & 1u, err, kErrWaitMma);
+                if (!ok) break;
+              }
 #pragma unroll
               for (int half = 0; half < 2; ++half) {
                 // P arrives in two halves of 64 keys: the first half of the product runs while the
                 // second half's exponentials are still being computed
                 ok = mbar_wait<0>(&ctl->p_ready[w][half], (pv_phase >> w) & 1u, err, kErrWaitMma);
                 if (!ok) break;
-                RSWA_TRC(fwd, j < 32, j * 32 + 1 + 4 * w + half);
+                RSWA_TRC(fwd, u >= 12 && u < 44, (u - 12) * 32 + 1 + 4 * w + half);
                 tc_fence_after();
 #pragma unroll
                 for (int k = 4 * half; k < 4 * half + 4; ++k) {
@@ -231,24 +293,38 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
               }
               if (!ok) break;
               mma_commit(&ctl->pv_done[w]);
-              RSWA_TRC(fwd, j < 32, j * 32 + 3 + 4 * w);
+              RSWA_TRC(fwd, u >= 12 && u < 44, (u - 12) * 32 + 3 + 4 * w);
               pv_phase ^= 1u << w;
               pv_any |= 1u << w;
             }
-            if ((f_nxt >> w) & 1u) {
-              // overwrites P_w of the current tile: ordered behind the product just issued
+            if ((f & kHasK) && ((f >> w) & 1u)) {
+              if (need_q) {  // the new item's Q (its load was issued right behind this unit's)
+                ok = mbar_wait<0>(&ctl->q_full, q_par, err, kErrWaitMma);
+                if (!ok) break;
+                tc_fence_after();
+                q_par ^= 1u;
+                need_q = false;
+              }
+              // overwrites P_w of the previous key tile: ordered behind the product just issued
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
                 const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
                 mma_ss(tSw, dQ + w * kTile16 + off, dKs + off, idesc_qk, k > 0 ? 1u : 0u);
               }
               mma_commit(&ctl->s_ready[w]);
-              RSWA_TRC(fwd, j < 32, j * 32 + 4 + 4 * w);
+              RSWA_TRC(fwd, u >= 12 && u < 44, (u - 12) * 32 + 4 + 4 * w);
             }
           }
           if (!ok) break;
           mma_commit(&ctl->kv_free[st]);
-          f_cur = f_nxt;
+          if (f & kLast) mma_commit(&ctl->q_free);  // that was the item's last read of Q
+          if ((f_prev & kLast) && (f & kHasV)) {
+            // the products above were the last of their item
+            if (pv_any & 1u) ++of_cnt0;
+            if (pv_any & 2u) ++of_cnt1;
+            pv_any = 0;
+          }
+          f_prev = (f & kHasK) ? f : 0u;
           if (st) kv_par ^= 1u;
         }
       }
@@ -263,181 +339,259 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tS = tmem + 128 * w + lane_off;
     const uint32_t tO = tmem + 256 + 128 * w + lane_off;
-    const bool valid = row < geom->n_valid[w];
-    const int pos = geom->p0[w] + row;
-    int s_p = 0, e_p = 0;
-    if (valid) seq_of(p.cu, p.n_seqs, pos, s_p, e_p);
-    // visible keys: [lo, hi] plus the sink positions [s_p, sink_end), all <= pos
-    const int hi = valid ? pos : -1;
-    const int lo = valid ? max(s_p, pos - p.window) : 0x7fffffff;
-    const int sink_end = valid ? s_p + p.n_sink : -0x7fffffff;
     const float sl2 = p.scale_log2;
-
-    float m_ref = -INFINITY;  // reference maximum in log2 units (already scaled)
-    float l_sum = 0.f;
-    int n_done = 0;           // key tiles this warp group has processed
+    uint8_t* stage = sStage + w * (kTileBytes / 2) + quad * 4096;  // this warp's 32 rows x 128 bytes
+    int n_tot = 0;   // key tiles this warp group has processed so far, all items (barrier phases)
     bool ok = true;
-    TileCursor cur;
-    cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (tile_active(geom, w, cur, p.n_sink)) {
-        const int kt0 = cur.kt0;
-        const int span_end = cur.kt_last + 1;
-        ok = mbar_wait(&ctl->s_ready[w], n_done & 1, err, kErrWaitSoftmax);
-        ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the TMEM accesses
-        if (!ok) break;
-        RSWA_TRC(fwd, lane == 0 && quad == 0 && j < 32, j * 32 + 10 + 8 * w);
-        tc_fence_after();
-        uint32_t r[128];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
-        tmem_ld_wait();
-        RSWA_TRC(fwd, lane == 0 && quad == 0 && j < 32, j * 32 + 11 + 8 * w);
-        // Mask.  Inside the tile this row sees the columns [c_lo, c_hi] (its window) and
-        // [s_lo, s_hi) (sink tokens that lie below the window).  Almost every masked tile is either the
-        // low edge of the band or the diagonal, where one compare per element is enough.
-        const int c_lo = lo - kt0;
-        const int c_hi = min(hi, span_end - 1) - kt0;
-        const int s_lo = s_p - kt0;
-        const int s_hi = min(min(sink_end, hi + 1), span_end) - kt0;
-        const bool sink_here = s_lo < s_hi && s_hi > 0 && s_lo < kTile && s_lo < c_lo;
-        if (__any_sync(0xffffffffu, sink_here)) {
-#pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            const bool vis = (i >= c_lo && i <= c_hi) || (i >= s_lo && i < s_hi);
-            if (!vis) r[i] = 0xff800000u;  // -inf
-          }
-        } else {
-          if (__any_sync(0xffffffffu, c_lo > 0)) {
-#pragma unroll
-            for (int i = 0; i < 128; ++i) r[i] = (i >= c_lo) ? r[i] : 0xff800000u;
-          }
-          if (__any_sync(0xffffffffu, c_hi < kTile - 1)) {
-#pragma unroll
-            for (int i = 0; i < 128; ++i) r[i] = (i <= c_hi) ? r[i] : 0xff800000u;
-          }
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 128; i += 8) {
-          mx0 = fmax3(mx0, __uint_as_float(r[i]), __uint_as_float(r[i + 4]));
-          mx1 = fmax3(mx1, __uint_as_float(r[i + 1]), __uint_as_float(r[i + 5]));
-          mx2 = fmax3(mx2, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 6]));
-          mx3 = fmax3(mx3, __uint_as_float(r[i + 3]), __uint_as_float(r[i + 7]));
-        }
-        // Lazy rescale: keep the old reference maximum unless the new one exceeds it by more than
-        // 2^8, so that O in TMEM is only touched rarely.
-        const float mt = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
-        float alpha = 1.f;
-        const bool grow = mt > m_ref + 8.f;
-        if (grow) {
-          alpha = ex2f(m_ref - mt);  // 0 when m_ref is -inf
-          m_ref = mt;
-        }
-        if (n_done > 0 && __any_sync(0xffffffffu, grow)) {
-          // O_w must be at rest: wait for the product of the previous tile
-          ok = mbar_wait(&ctl->pv_done[w], (n_done - 1) & 1, err, kErrWaitSoftmax);
-          ok = __all_sync(0xffffffffu, ok);
+
+    for (int n = 0; ok; ++n) {
+      const int slot = n & 1;
+      ok = mbar_wait(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitSoftmax);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int it = ctl->item[slot];
+      if (it < 0) break;
+      const FwdItem wi = fwd_item(p, n_blocks, it);
+      const QBlockGeom* geom = &ctl->geom[slot];
+      const int n_tiles = geom->n_tiles;
+      const bool valid = row < geom->n_valid[w];
+      const int pos = geom->p0[w] + row;
+      int s_p = 0, e_p = 0;
+      // (rows past the end look their sequence up at the last row that exists, so that s_p grows with the row)
+      seq_of(p.cu, p.n_seqs, geom->p0[w] + min(row, max(geom->n_valid[w], 1) - 1), s_p, e_p);
+      // visible keys: [lo, hi] plus the sink positions [s_p, sink_end), all <= pos; nothing for rows
+      // that do not exist
+      const int hi = valid ? pos : -1;
+      const int lo = valid ? max(s_p, pos - p.window) : 0x7fffffff;
+      const int sink_end = valid ? s_p + p.n_sink : -0x7fffffff;
+      // warp-uniform bounds for choosing the mask path of each 32-column chunk without a vote (a warp
+      // with rows that do not exist gets bounds that send every chunk down the per-element path)
+      const int lo_min = __reduce_min_sync(0xffffffffu, lo), lo_max = __reduce_max_sync(0xffffffffu, lo);
+      const int hi_min = __reduce_min_sync(0xffffffffu, hi), hi_max = __reduce_max_sync(0xffffffffu, hi);
+      const int sp_first = __shfl_sync(0xffffffffu, s_p, 0);
+      const int se_last = __shfl_sync(0xffffffffu, s_p, 31) + p.n_sink;
+
+      float m_ref = -INFINITY;  // reference maximum in log2 units (already scaled)
+      float l_sum = 0.f;
+      int n_done = 0;           // key tiles of this item this warp group has processed
+      TileCursor cur;
+      cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (tile_active(geom, w, cur, p.n_sink)) {
+          const int kt0 = cur.kt0;
+          const int span_end = cur.kt_last + 1;
+          ok = mbar_wait(&ctl->s_ready[w], n_tot & 1, err, kErrWaitSoftmax);
+          ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the TMEM accesses
           if (!ok) break;
+          RSWA_TRC(fwd, lane == 0 && quad == 0 && n == 1 && j < 32, j * 32 + 10 + 8 * w);
           tc_fence_after();
-          l_sum *= alpha;
+          // Mask geometry.  Inside the tile this row sees the columns [c_lo, c_hi] (its window) and,
+          // with sink tokens below the window, [s_lo, s_lo + sn).  The tile is handled in chunks of 32
+          // columns, in two short rolled loops (row maximum, then exponentials) that reload the chunk
+          // from tensor memory: straight-line code over all 128 columns is several times larger than
+          // the instruction cache next to the schedulers and ran at a quarter of the issue rate.
+          // A chunk every row of the warp sees needs no masking, a chunk no row sees is dropped whole
+          // (no exponentials either), only the chunks the band edge or the diagonal crosses pay the
+          // compares.
+          const int c_lo = lo - kt0;
+          const int c_hi = min(hi, span_end - 1) - kt0;
+          const bool sink_tile = p.n_sink > 0 && kt0 < se_last && kt0 + kTile > sp_first;
+          const uint32_t wn = static_cast<uint32_t>(max(c_hi - c_lo + 1, 0));
+          const int s_lo = s_p - kt0;
+          const uint32_t sn = static_cast<uint32_t>(max(min(min(sink_end, hi + 1), span_end) - kt0 - s_lo, 0));
+          const int top_all = min(hi_min, span_end - 1), top_any = min(hi_max, span_end - 1);
+          uint32_t dead = 0, part = 0;  // bit c: no row of this warp sees chunk c / some rows see part of it
+          if (sink_tile) {
+            part = 15u;
+          } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int a = kt0 + 32 * c, b = a + 31;
+              if (b < lo_min || a > top_any) dead |= 1u << c;
+              else if (a < lo_max || b > top_all) part |= 1u << c;
+            }
+          }
+          auto mask_chunk = [&](int c, uint32_t (&r)[32]) {
+            if (part & (1u << c)) {
+              if (sink_tile) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  const int col = c * 32 + i;
+                  const bool vis = static_cast<uint32_t>(col - c_lo) < wn || static_cast<uint32_t>(col - s_lo) < sn;
+                  r[i] = vis ? r[i] : 0xff800000u;  // -inf
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  const int col = c * 32 + i;
+                  r[i] = (col >= c_lo && col <= c_hi) ? r[i] : 0xff800000u;
+                }
+              }
+            }
+          };
+          // pass 1: the row maximum
+          float mx = -INFINITY;
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tO + c * 32, o);
+            if (dead & (1u << c)) continue;
+            uint32_t r[32];
+            tmem_ld32(tS + c * 32, r);
             tmem_ld_wait();
+            mask_chunk(c, r);
+            float m0 = fmax3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+            float m1 = fmax3(__uint_as_float(r[3]), __uint_as_float(r[4]), __uint_as_float(r[5]));
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tO + c * 32, o);
+            for (int i = 6; i < 30; i += 6) {
+              m0 = fmax3(m0, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+              m1 = fmax3(m1, __uint_as_float(r[i + 3]), __uint_as_float(r[i + 4]));
+              m0 = fmaxf(m0, __uint_as_float(r[i + 2]));
+              m1 = fmaxf(m1, __uint_as_float(r[i + 5]));
+            }
+            m0 = fmax3(m0, __uint_as_float(r[30]), __uint_as_float(r[31]));
+            mx = fmax3(mx, m0, m1);
           }
-          tmem_st_wait();
-        }
-        RSWA_TRC(fwd, lane == 0 && quad == 0 && j < 32, j * 32 + 12 + 8 * w);
-        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-        const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(-m_use, -m_use);
-        float2 lacc = make_float2(0.f, 0.f);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[c * 32 + i]), __uint_as_float(r[c * 32 + i + 1])),
-                                        sl2v, nmv);
-            const float2 e = make_float2(ex2f(x.x), ex2f(x.y));
-            lacc = __fadd2_rn(lacc, e);
-            pk[i >> 1] = pack2<kBf16>(e.x, e.y);
+          RSWA_TRC(fwd, lane == 0 && quad == 0 && n == 1 && j < 32, j * 32 + 11 + 8 * w);
+          // Lazy rescale: keep the old reference maximum unless the new one exceeds it by more than
+          // 2^8, so that O in TMEM is only touched rarely.
+          const float mt = mx * sl2;
+          float alpha = 1.f;
+          const bool grow = mt > m_ref + 8.f;
+          if (grow) {
+            alpha = ex2f(m_ref - mt);  // 0 when m_ref is -inf
+            m_ref = mt;
           }
-          tmem_st16(tS + c * 16, pk);
-          if (c & 1) {
-            // a half of P (64 keys) is complete: its share of O_w += P_w V may start
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl->p_ready[w][c >> 1]);
-            RSWA_TRC(fwd, lane == 0 && quad == 0 && j < 32, j * 32 + 13 + 8 * w + (c >> 1));
-          }
-        }
-        l_sum += lacc.x + lacc.y;
-        ++n_done;
-      }
-      cursor_next<kTile>(geom, p.span_pos, p.span_len, cur, j + 1 < n_tiles);
-    }
-
-    // epilogue: O / l -> out, lse
-    RSWA_TRC(fwd, lane == 0 && quad == 0, 1924 + 4 * w);
-    if (ok && n_done > 0) ok = mbar_wait(&ctl->pv_done[w], (n_done - 1) & 1, err, kErrWaitEpilogue);
-    ok = __all_sync(0xffffffffu, ok);
-    RSWA_TRC(fwd, lane == 0 && quad == 0, 1925 + 4 * w);
-    tc_fence_after();
-    const bool has = ok && n_done > 0 && l_sum > 0.f;
-    const float inv = has ? 1.f / l_sum : 0.f;
-    const int grow_q = (tile0 + w) * kTile + row;  // row inside the local q tensor
-    if (n_done > 0 && ok) {
-      // The rows go out through shared memory: a thread owns one 256-byte row, so storing from
-      // registers would touch 32 different lines per instruction.  Staged in this warp's quarter of
-      // the (no longer needed) Q tile, 16-byte chunks XOR-swizzled by row, each instruction then
-      // writes two whole rows.  Only this warp touches the quarter: a warp-level sync suffices.
-      uint8_t* stage = sQ + w * kTileBytes + quad * (32 * 256);
+          if (n_done > 0 && __any_sync(0xffffffffu, grow)) {
+            // O_w must be at rest: wait for the product of the previous tile
+            ok = mbar_wait(&ctl->pv_done[w], (n_tot - 1) & 1, err, kErrWaitSoftmax);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            l_sum *= alpha;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tO + c * 32, o);
-        tmem_ld_wait();
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tO + c * 32, o);
+              tmem_ld_wait();
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 q4;
-          q4.x = pack2<kBf16>(__uint_as_float(o[v * 8 + 0]) * inv, __uint_as_float(o[v * 8 + 1]) * inv);
-          q4.y = pack2<kBf16>(__uint_as_float(o[v * 8 + 2]) * inv, __uint_as_float(o[v * 8 + 3]) * inv);
-          q4.z = pack2<kBf16>(__uint_as_float(o[v * 8 + 4]) * inv, __uint_as_float(o[v * 8 + 5]) * inv);
-          q4.w = pack2<kBf16>(__uint_as_float(o[v * 8 + 6]) * inv, __uint_as_float(o[v * 8 + 7]) * inv);
-          if (!has) q4 = make_uint4(0, 0, 0, 0);  // a row without a visible key
-          *reinterpret_cast<uint4*>(stage + lane * 256 + (((c * 4 + v) ^ (lane & 15)) << 4)) = q4;
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + c * 32, o);
+            }
+            tmem_st_wait();
+          }
+          RSWA_TRC(fwd, lane == 0 && quad == 0 && n == 1 && j < 32, j * 32 + 12 + 8 * w);
+          const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+          const float2 sl2v = make_float2(sl2, sl2), nmv = make_float2(-m_use, -m_use);
+          float2 lacc = make_float2(0.f, 0.f);
+          // pass 2: exponentials, 32 columns at a time
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t pk[16];
+            if (dead & (1u << c)) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pk[i] = 0u;
+            } else {
+              uint32_t r[32];
+              tmem_ld32(tS + c * 32, r);
+              tmem_ld_wait();
+              mask_chunk(c, r);
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), sl2v, nmv);
+                // one pair in kPolyEvery goes through the FMA pipe instead of the special-function unit,
+                // which would otherwise need as long for a tile's exponentials as the tensor cores for
+                // its two products
+                const float2 e = (kPolyEvery > 0 && ((i >> 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == (kPolyEvery - 1))
+                                     ? ex2_poly2(x) : make_float2(ex2f(x.x), ex2f(x.y));
+                lacc = __fadd2_rn(lacc, e);
+                pk[i >> 1] = pack2<kBf16>(e.x, e.y);
+              }
+            }
+            // P (16-bit) goes over the first half of the S columns, all of which this warp has read by now
+            tmem_st16(tS + c * 16, pk);
+            if (c & 1) {
+              // a half of P (64 keys) is complete: its share of O_w += P_w V may start
+              tmem_st_wait();
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&ctl->p_ready[w][c >> 1]);
+              RSWA_TRC(fwd, lane == 0 && quad == 0 && n == 1 && j < 32, j * 32 + 13 + 8 * w + (c >> 1));
+            }
+          }
+          l_sum += lacc.x + lacc.y;
+          ++n_done;
+          ++n_tot;
         }
+        cursor_next<kTile>(geom, p.span_pos, p.span_len, cur, j + 1 < n_tiles);
       }
-      __syncwarp();
+      if (!ok) break;
+
+      // epilogue: O / l -> out, lse
+      RSWA_TRC(fwd, lane == 0 && quad == 0 && n == 1, 1924 + 4 * w);
       const int n_rows = geom->n_valid[w] - quad * 32;  // rows of this warp that exist
-      uint16_t* obase = reinterpret_cast<uint16_t*>(p.out) + b * p.o_sb +
-                        static_cast<long long>((tile0 + w) * kTile + quad * 32) * p.o_st + h * p.o_sh;
-      const int ch = lane & 15;
-#pragma unroll 4
-      for (int i = 0; i < 16; ++i) {
-        const int r = 2 * i + (lane >> 4);
-        const uint4 q4 = *reinterpret_cast<const uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4));
-        if (r < n_rows) *reinterpret_cast<uint4*>(obase + static_cast<long long>(r) * p.o_st + ch * 8) = q4;
-      }
-    } else if (valid) {
-      // no key of the given spans is visible to this query tile: zero rows
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + b * p.o_sb +
-                                            static_cast<long long>(grow_q) * p.o_st + h * p.o_sh);
+      const int tile_row0 = (wi.tile0 + w) * kTile;     // first row of the tile inside the local q tensor
+      // (a row whose every score was masked keeps m_ref = -inf; the exponentials computed on the FMA pipe
+      // leave l_sum a hair above zero for it, so the row sum is no test)
+      const bool has = n_done > 0 && m_ref > -INFINITY && l_sum > 0.f;
+      const float inv = has ? 1.f / l_sum : 0.f;
+      if (n_done > 0) {
+        ok = mbar_wait(&ctl->pv_done[w], (n_tot - 1) & 1, err, kErrWaitEpilogue);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        RSWA_TRC(fwd, lane == 0 && quad == 0 && n == 1, 1925 + 4 * w);
+        tc_fence_after();
+        uint32_t o[128];
 #pragma unroll
-      for (int v = 0; v < 16; ++v) dst[v] = make_uint4(0, 0, 0, 0);
-    }
-    if (valid) {
-      p.lse[b * p.l_sb + h * p.l_sh + grow_q] = has ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+        for (int c = 0; c < 4; ++c) tmem_ld32(tO + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[c * 32]));
+        tmem_ld_wait();
+        // the accumulator is in registers: the next item's first product may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->o_free[w]);
+        // The rows go out through shared memory: a thread owns one 256-byte row, so storing from
+        // registers would touch 32 different lines per instruction.  Staged in two passes of 128 bytes
+        // per row (16-byte chunks XOR-swizzled by row), each store instruction then writes four
+        // 128-byte row segments.  Only this warp touches its part of the staging buffer.
+        uint16_t* obase = reinterpret_cast<uint16_t*>(p.out) + wi.b * p.o_sb +
+                          static_cast<long long>(tile_row0 + quad * 32) * p.o_st + wi.h * p.o_sh;
+        const int ch = lane & 7;
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const int e0 = pass * 64 + v * 8;
+            uint4 q4;
+            q4.x = pack2<kBf16>(__uint_as_float(o[e0 + 0]) * inv, __uint_as_float(o[e0 + 1]) * inv);
+            q4.y = pack2<kBf16>(__uint_as_float(o[e0 + 2]) * inv, __uint_as_float(o[e0 + 3]) * inv);
+            q4.z = pack2<kBf16>(__uint_as_float(o[e0 + 4]) * inv, __uint_as_float(o[e0 + 5]) * inv);
+            q4.w = pack2<kBf16>(__uint_as_float(o[e0 + 6]) * inv, __uint_as_float(o[e0 + 7]) * inv);
+            *reinterpret_cast<uint4*>(stage + lane * 128 + ((v ^ (lane & 7)) << 4)) = q4;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + (lane >> 3);
+            const uint4 q4 = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((ch ^ (rr & 7)) << 4));
+            if (rr < n_rows) *reinterpret_cast<uint4*>(obase + static_cast<long long>(rr) * p.o_st + pass * 64 + ch * 8) = q4;
+          }
+          __syncwarp();  // the staging rows are rewritten by the next pass / item
+        }
+      } else if (valid) {
+        // no key of the given spans is visible to this query tile: zero rows
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + wi.b * p.o_sb +
+                                              static_cast<long long>(tile_row0 + row) * p.o_st + wi.h * p.o_sh);
+#pragma unroll
+        for (int v = 0; v < 16; ++v) dst[v] = make_uint4(0, 0, 0, 0);
+      }
+      if (valid) {
+        p.lse[wi.b * p.l_sb + wi.h * p.l_sh + tile_row0 + row] =
+            has ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+      }
+      RSWA_TRC(fwd, lane == 0 && quad == 0 && n == 1, 1926 + 4 * w);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->geom_free[slot]);
     }
   }
 
-  RSWA_TRC(fwd, lane == 0 && (warp == 4 || warp == 8), 1926 + (warp == 8 ? 4 : 0));
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -451,10 +605,11 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p) {
 }  // namespace
 
 int launch_fwd(const FwdKernelParams& kp, int dtype, cudaStream_t stream) {
-  const long long n_cta = static_cast<long long>((kp.n_q_tiles + 1) / 2) * kp.hq * kp.batch;
-  if (n_cta <= 0) return RSWA_OK;
-  if (n_cta > 0x7fffffffLL) {
-    set_error("rswa_fwd: too many query tiles (%lld)", n_cta);
+  const int n_blocks = (kp.n_q_tiles + 1) / 2;
+  const long long n_items = static_cast<long long>(n_blocks) * kp.hq * kp.batch;
+  if (n_items <= 0) return RSWA_OK;
+  if (n_items > 0x7fffffffLL) {
+    set_error("rswa_fwd: too many query tiles (%lld)", n_items);
     return RSWA_E_ARG;
   }
   auto kern = dtype == RSWA_DTYPE_BF16 ? rswa_fwd_kernel<true> : rswa_fwd_kernel<false>;
@@ -463,7 +618,9 @@ int launch_fwd(const FwdKernelParams& kp, int dtype, cudaStream_t stream) {
     set_error("rswa_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return RSWA_E_CUDA;
   }
-  kern<<<static_cast<unsigned>(n_cta), kFwdThreads, kFwdSmemBytes, stream>>>(kp);
+  // one CTA per SM (shared memory and TMEM allow no more), each striding over the items
+  const long long n_cta = n_items < sm_count() ? n_items : sm_count();
+  kern<<<static_cast<unsigned>(n_cta), kFwdThreads, kFwdSmemBytes, stream>>>(kp, n_blocks, static_cast<int>(n_items));
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("rswa_fwd: launch: %s", cudaGetErrorString(e));

@@ -294,6 +294,23 @@ __device__ __forceinline__ float ex2f(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for two values on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a cubic
+// (max relative error 7.5e-5, well below the 16-bit rounding P gets afterwards), 2^n by adding n to the
+// exponent field.  Inputs below -125 (masked scores are -inf) give 2^-125.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));  // 1.5 * 2^23: n lands in the low mantissa bits
+  const float2 nf = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(nf, make_float2(-1.f, -1.f), x);
+  float2 q = __ffma2_rn(make_float2(0.0551716648f, 0.0551716648f), f, make_float2(0.2426111251f, 0.2426111251f));
+  q = __ffma2_rn(q, f, make_float2(0.6932609677f, 0.6932609677f));
+  q = __ffma2_rn(q, f, make_float2(0.9999280572f, 0.9999280572f));
+  float2 r;
+  r.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(t.x) << 23));
+  r.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(t.y) << 23));
+  return r;
+}
 // max of three (one instruction on sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
