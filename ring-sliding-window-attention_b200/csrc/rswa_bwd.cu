@@ -16,30 +16,38 @@
 // rowsum(dO * O), which is what makes a per-span backward against the FINAL out/lse exact (the
 // property the reference's per-hop backward relies on, ring_swa/ops/attn.py:63-126).
 //
-// Pipeline: S^T of the next query tile is issued as soon as the compute warps have read the
-// current one out of TMEM, dP^T of the next tile right behind dV/dK of the current one, so the
-// exponentials of tile i+1 overlap the products of tile i.  Q tiles travel through a 3-stage ring
-// (they are needed one tile ahead), dO tiles through a 2-stage ring.  Two warps issue MMAs.
+// Pipeline: one thread issues every product, in the order  dV(i), dK(i), dP^T(i+1), S^T(i+2)  once
+// P^T | dS^T of query tile i are in tensor memory: dP^T(i+1) overwrites their columns, which issue
+// order makes safe without a wait, and S^T(i+2) fills the tensor pipe while the compute warps turn
+// dP^T(i+1) into dS^T(i+1).  The exponentials of tile i+1 run off that critical loop.  Q tiles travel
+// through a 3-stage ring (they are needed two tiles ahead), dO tiles through a 2-stage ring.
 // TMEM columns: [0,128) dK, [128,256) dV, [256,384) S^T, [384,512) dP^T, over which each compute
 // warp writes P^T and dS^T of the 64 query columns it has just read (P^T in the first 32 of its 64
-// columns, dS^T in the other 32).  dK and dV leave through shared memory as whole row segments.
+// columns, dS^T in the other 32), handed over in two chunks of 32 queries.  dK and dV leave through
+// shared memory as whole row segments.
 #include "rswa_common.cuh"
 #include "tc05.cuh"
 
 namespace rswa {
 using namespace tc05;
 
+RSWA_TRACE_DECL(bwd)
+
 namespace {
 
-constexpr int kBwdThreads = 384;  // warp 0 TMA, warps 1-2 MMA, warp 3 idle, warps 4-11 compute
+constexpr int kBwdThreads = 384;  // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-11 compute
 constexpr int kMmaPollNs = 0;  // the MMA-issuing threads poll without back-off (they are on the critical path)
 constexpr int kBwdTmemCols = 512;
 constexpr int kComputeThreads = 256;
 constexpr int kQStages = 3;
+#ifndef RSWA_BWD_POLY
+#define RSWA_BWD_POLY 1
+#endif
+constexpr bool kBwdPoly = RSWA_BWD_POLY != 0;  // a quarter of the exponentials on the FMA pipe
 
 struct BwdCtl {
   uint64_t kv_full, q_full[kQStages], q_free[kQStages], do_full[2], do_free[2];
-  uint64_t s_ready, s_loaded, dp_ready, pds_ready, dv_done, done;
+  uint64_t s_ready, s_loaded, dp_ready, pds_ready[2], done;
   uint32_t tmem_base;
   int err;
   int qt_first, n_qt;
@@ -66,6 +74,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   float* sDelta = sLse + kQStages * kTile;                       // [2][128], travels with dO
   BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + kBwdSmemTiles + (kQStages + 2) * kRowBytes);
 
+  RSWA_TRC(bwd, threadIdx.x == 0, 1920);
   // Has a device-side error already been reported on this stream?  Then this CTA does no work (no
   // further time-outs piled on the first).  The word is read now and looked at after the set-up
   // below, so that its latency is not paid at the head of every CTA.
@@ -107,9 +116,9 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     mbar_init(&ctl->s_ready, 1);
     mbar_init(&ctl->s_loaded, kComputeThreads / 32);  // one arrival per compute warp
     mbar_init(&ctl->dp_ready, 1);
-    mbar_init(&ctl->pds_ready, kComputeThreads / 32);
-    mbar_init(&ctl->dv_done, 1);
-    mbar_init(&ctl->done, 2);
+    mbar_init(&ctl->pds_ready[0], kComputeThreads / 32);  // one arrival per compute warp and chunk of 32 queries
+    mbar_init(&ctl->pds_ready[1], kComputeThreads / 32);
+    mbar_init(&ctl->done, 1);
     mbar_fence_init();
     // K and V of this tile depend on nothing computed below: they are on their way while the rest
     // of the set-up runs (the CTA waits for them before it exits even if it has no work)
@@ -147,6 +156,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   __syncthreads();
   tc_fence_after();
 
+  RSWA_TRC(bwd, threadIdx.x == 0, 1921);
   const uint32_t tmem = ctl->tmem_base;
   const uint32_t tDK = tmem, tDV = tmem + 128, tS = tmem + 256, tB = tmem + 384;
   volatile int* err = &ctl->err;
@@ -156,7 +166,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
   constexpr uint32_t kTile16 = kTileBytes >> 4;
 
   if (warp < 4) {
-    setmaxnreg_dec<64>();
+    setmaxnreg_dec<80>();
     if (warp == 0 && lane == 0 && n_iter > 0) {
       // ------------------------------------------------------------------ TMA producer
       bool ok = true;
@@ -178,105 +188,91 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         tma_load_4d(sDO + sd * kTileBytes + kBoxBytes, &p.do_map, &ctl->do_full[sd], 64, h, row0, b);
         bulk_load_1d(sDelta + sd * kTile, p.delta + roff, kRowBytes, &ctl->do_full[sd]);
       }
-    } else if (warp == 1 && n_iter > 0) {
-      // ------------------------------------------------------------------ MMA issuer 1: S^T and dV
-      // (all 32 lanes run the loop, one elected lane issues: a converged warp keeps its share of the
-      // issue slots when the compute warps beside it are in an FMA-heavy phase, a lone lane does not)
+    } else if (warp == 1 && n_iter > 0 && elect_one()) {
+      // ------------------------------------------------------------------ MMA issuer
+      // ONE elected thread issues every product and does all the waiting for them (a warp-wide vote
+      // behind each wait costs more than it saves).  Steady-state order, once P^T | dS^T of tile i is
+      // in tensor memory:   dV(i), dK(i), dP^T(i+1), S^T(i+2).
+      // dP^T(i+1) overwrites the columns that hold P^T | dS^T of tile i; products of one thread execute
+      // in issue order, so it needs no wait for dV(i) and dK(i).  S^T(i+2) goes last: nothing on the
+      // loop that bounds the kernel needs it soon, and there it fills the tensor pipe while the compute
+      // warps turn dP^T(i+1) into dS^T(i+1) (issued from a second thread it interleaved with the three
+      // products ahead of it and delayed them by a third).
       constexpr int bf = kBf16 ? 1 : 0;
       constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);  // both operands K-major
       constexpr uint32_t id_tn = idesc_f16(128, 128, bf, 0, 1);  // A from TMEM, B MN-major
       const uint64_t dK = smem_desc_sw128(smem_u32(sK), 16, 1024);
-      const uint64_t dQk = smem_desc_sw128(smem_u32(sQ), 16, 1024);
-      const uint64_t dDOm = smem_desc_sw128(smem_u32(sDO), kBoxBytes, 1024);
-      bool ok = mbar_wait_w<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->q_full[0], 0, err, kErrWaitMma);
-      if (ok) {
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-          mma_ss_w(tS, dK + off, dQk + off, id_kk, k > 0 ? 1u : 0u);
-        }
-        mma_commit_w(&ctl->s_ready);
-      }
-      for (int it = 0; it < n_iter && ok; ++it) {
-        if (it + 1 < n_iter) {
-          // S^T of the next query tile, once every compute warp holds the current one in registers
-          const int sq = (it + 1) % kQStages;
-          ok = mbar_wait_w<kMmaPollNs>(&ctl->q_full[sq], ((it + 1) / kQStages) & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->s_loaded, it & 1, err, kErrWaitMma);
-          if (!ok) break;
-          tc_fence_after();
-          const uint64_t dQs = dQk + sq * kTile16;
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-            mma_ss_w(tS, dK + off, dQs + off, id_kk, k > 0 ? 1u : 0u);
-          }
-          mma_commit_w(&ctl->s_ready);
-        }
-        ok = mbar_wait_w<kMmaPollNs>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t dDOs = dDOm + (it & 1) * kTile16;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dV += P^T dO
-          mma_ts_w(tDV, tB + (k >> 2) * 64 + (k & 3) * 8, dDOs + k * 128, id_tn, (it > 0 || k > 0) ? 1u : 0u);
-        }
-        mma_commit_w(&ctl->dv_done);
-        mma_commit_w(&ctl->do_free[it & 1]);
-      }
-      if (ok) mma_commit_w(&ctl->done);
-    } else if (warp == 2 && n_iter > 0) {
-      // ------------------------------------------------------------------ MMA issuer 2: dP^T and dK
-      constexpr int bf = kBf16 ? 1 : 0;
-      constexpr uint32_t id_kk = idesc_f16(128, 128, bf, 0, 0);
-      constexpr uint32_t id_tn = idesc_f16(128, 128, bf, 0, 1);
       const uint64_t dV = smem_desc_sw128(smem_u32(sV), 16, 1024);
-      const uint64_t dDOk = smem_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t dQk = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t dQm = smem_desc_sw128(smem_u32(sQ), kBoxBytes, 1024);
-      bool ok = mbar_wait_w<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
-      if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->do_full[0], 0, err, kErrWaitMma);
-      if (ok) {
+      const uint64_t dDOk = smem_desc_sw128(smem_u32(sDO), 16, 1024);
+      const uint64_t dDOm = smem_desc_sw128(smem_u32(sDO), kBoxBytes, 1024);
+      auto issue_s = [&](int t) -> bool {  // S^T of query tile t, once the compute warps hold tile t - 1 in registers
+        const int sq = t % kQStages;
+        if (!mbar_wait<kMmaPollNs>(&ctl->q_full[sq], (t / kQStages) & 1, err, kErrWaitMma)) return false;
+        if (t > 0 && !mbar_wait<kMmaPollNs>(&ctl->s_loaded, (t - 1) & 1, err, kErrWaitMma)) return false;
         tc_fence_after();
+        const uint64_t dQs = dQk + sq * kTile16;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-          mma_ss_w(tB, dV + off, dDOk + off, id_kk, k > 0 ? 1u : 0u);
+          mma_ss(tS, dK + off, dQs + off, id_kk, k > 0 ? 1u : 0u);
         }
-        mma_commit_w(&ctl->dp_ready);
-      }
-      for (int it = 0; it < n_iter && ok; ++it) {
-        ok = mbar_wait_w<kMmaPollNs>(&ctl->pds_ready, it & 1, err, kErrWaitMma);
-        if (!ok) break;
+        mma_commit(&ctl->s_ready);
+        return true;
+      };
+      auto issue_dp = [&](int t) -> bool {  // dP^T of query tile t (the caller has ordered it behind the readers of tB)
+        const int sd = t & 1;
+        if (!mbar_wait<kMmaPollNs>(&ctl->do_full[sd], (t >> 1) & 1, err, kErrWaitMma)) return false;
         tc_fence_after();
+        const uint64_t dDOs = dDOk + sd * kTile16;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
+          mma_ss(tB, dV + off, dDOs + off, id_kk, k > 0 ? 1u : 0u);
+        }
+        mma_commit(&ctl->dp_ready);
+        return true;
+      };
+      bool ok = mbar_wait<kMmaPollNs>(&ctl->kv_full, 0, err, kErrWaitMma);
+      if (ok) ok = issue_s(0);
+      if (ok) ok = issue_dp(0);
+      if (ok && n_iter > 1) ok = issue_s(1);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint64_t dDOs = dDOm + (it & 1) * kTile16;
         const uint64_t dQs = dQm + (it % kQStages) * kTile16;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dK += dS^T Q
-          mma_ts_w(tDK, tB + (k >> 2) * 64 + 32 + (k & 3) * 8, dQs + k * 128, id_tn, (it > 0 || k > 0) ? 1u : 0u);
-        }
-        mma_commit_w(&ctl->q_free[it % kQStages]);
-        if (it + 1 < n_iter) {
-          // dP^T of the next tile overwrites P^T | dS^T: behind dK (this thread) and dV (the other)
-          const int sd = (it + 1) & 1;
-          ok = mbar_wait_w<kMmaPollNs>(&ctl->do_full[sd], ((it + 1) >> 1) & 1, err, kErrWaitMma);
-          if (ok) ok = mbar_wait_w<kMmaPollNs>(&ctl->dv_done, it & 1, err, kErrWaitMma);
+        for (int ch = 0; ch < 2; ++ch) {
+          // P^T | dS^T arrive in two chunks: every compute warp's first 32 query columns (k-steps
+          // 0, 1, 4, 5 of the 128 queries), then its other 32 (k-steps 2, 3, 6, 7)
+          ok = mbar_wait<kMmaPollNs>(&ctl->pds_ready[ch], it & 1, err, kErrWaitMma);
           if (!ok) break;
+          RSWA_TRC(bwd, it < 32 && ch == 0, it * 32 + 8);
           tc_fence_after();
-          const uint64_t dDOs = dDOk + sd * kTile16;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-            mma_ss_w(tB, dV + off, dDOs + off, id_kk, k > 0 ? 1u : 0u);
+          for (int kk = 0; kk < 4; ++kk) {  // dV += P^T dO
+            const int k = (kk >> 1) * 4 + 2 * ch + (kk & 1);
+            mma_ts(tDV, tB + (k >> 2) * 64 + (k & 3) * 8, dDOs + k * 128, id_tn, (it > 0 || ch > 0 || kk > 0) ? 1u : 0u);
           }
-          mma_commit_w(&ctl->dp_ready);
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {  // dK += dS^T Q
+            const int k = (kk >> 1) * 4 + 2 * ch + (kk & 1);
+            mma_ts(tDK, tB + (k >> 2) * 64 + 32 + (k & 3) * 8, dQs + k * 128, id_tn, (it > 0 || ch > 0 || kk > 0) ? 1u : 0u);
+          }
         }
+        if (!ok) break;
+        mma_commit(&ctl->do_free[it & 1]);         // (dP^T of this tile, the stage's other reader, was issued before)
+        mma_commit(&ctl->q_free[it % kQStages]);   // (S^T of this tile, the stage's other reader, was issued before)
+        RSWA_TRC(bwd, it < 32, it * 32 + 9);
+        if (it + 1 < n_iter) ok = issue_dp(it + 1);
+        RSWA_TRC(bwd, it < 32, it * 32 + 11);
+        if (ok && it + 2 < n_iter) ok = issue_s(it + 2);
       }
-      if (ok) mma_commit_w(&ctl->done);
+      if (ok) mma_commit(&ctl->done);
     }
   } else {
     // -------------------------------------------------------------------- compute warps
-    setmaxnreg_inc<216>();  // 128 x 64 + 256 x 216 <= 384 x 168 (the launch allocation)
+    setmaxnreg_inc<208>();  // 128 x 80 + 256 x 208 <= 384 x 168 (the launch allocation)
     const int quad = warp & 3;
     const int half = (warp - 4) >> 2;            // which 64 query columns this warp handles
     const int row = quad * 32 + lane;            // key row
@@ -306,6 +302,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
       ok = mbar_wait(&ctl->s_ready, it & 1, err, kErrWaitSoftmax);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      RSWA_TRC(bwd, warp == 4 && lane == 0 && it < 32, it * 32 + 0);
       tc_fence_after();
       float pr[64];
       {
@@ -320,14 +317,20 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         for (int i = 0; i < 32; i += 4) {
           const float4 la = *reinterpret_cast<const float4*>(lse_s + i);
           const float4 lb = *reinterpret_cast<const float4*>(lse_s + i + 32);
-          pr[i + 0] = ex2f(fmaf(__uint_as_float(s0[i + 0]), sl2, -la.x));
-          pr[i + 1] = ex2f(fmaf(__uint_as_float(s0[i + 1]), sl2, -la.y));
-          pr[i + 2] = ex2f(fmaf(__uint_as_float(s0[i + 2]), sl2, -la.z));
-          pr[i + 3] = ex2f(fmaf(__uint_as_float(s0[i + 3]), sl2, -la.w));
-          pr[i + 32] = ex2f(fmaf(__uint_as_float(s1[i + 0]), sl2, -lb.x));
-          pr[i + 33] = ex2f(fmaf(__uint_as_float(s1[i + 1]), sl2, -lb.y));
-          pr[i + 34] = ex2f(fmaf(__uint_as_float(s1[i + 2]), sl2, -lb.z));
-          pr[i + 35] = ex2f(fmaf(__uint_as_float(s1[i + 3]), sl2, -lb.w));
+          const float xa0 = fmaf(__uint_as_float(s0[i + 0]), sl2, -la.x), xa1 = fmaf(__uint_as_float(s0[i + 1]), sl2, -la.y);
+          const float xa2 = fmaf(__uint_as_float(s0[i + 2]), sl2, -la.z), xa3 = fmaf(__uint_as_float(s0[i + 3]), sl2, -la.w);
+          const float xb0 = fmaf(__uint_as_float(s1[i + 0]), sl2, -lb.x), xb1 = fmaf(__uint_as_float(s1[i + 1]), sl2, -lb.y);
+          const float xb2 = fmaf(__uint_as_float(s1[i + 2]), sl2, -lb.z), xb3 = fmaf(__uint_as_float(s1[i + 3]), sl2, -lb.w);
+          // one pair in four goes through the FMA pipe instead of the special-function unit
+          pr[i + 0] = ex2f(xa0), pr[i + 1] = ex2f(xa1);
+          pr[i + 32] = ex2f(xb0), pr[i + 33] = ex2f(xb1);
+          if (kBwdPoly && (i & 4)) {
+            const float2 ea = ex2_poly2(make_float2(xa2, xa3)), eb = ex2_poly2(make_float2(xb2, xb3));
+            pr[i + 2] = ea.x, pr[i + 3] = ea.y, pr[i + 34] = eb.x, pr[i + 35] = eb.y;
+          } else {
+            pr[i + 2] = ex2f(xa2), pr[i + 3] = ex2f(xa3);
+            pr[i + 34] = ex2f(xb2), pr[i + 35] = ex2f(xb3);
+          }
         }
       }
       if (masked) {
@@ -358,34 +361,47 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
         npd[i + 32] = -pr[i + 32] * db.x, npd[i + 33] = -pr[i + 33] * db.y;
         npd[i + 34] = -pr[i + 34] * db.z, npd[i + 35] = -pr[i + 35] * db.w;
       }
+      RSWA_TRC(bwd, warp == 4 && lane == 0 && it < 32, it * 32 + 1);
       ok = mbar_wait(&ctl->dp_ready, it & 1, err, kErrWaitSoftmax);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      RSWA_TRC(bwd, warp == 4 && lane == 0 && it < 32, it * 32 + 2);
       tc_fence_after();
-      uint32_t dpk[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t d[32];
-        tmem_ld32(tB + lane_off + half * 64 + c * 32, d);
+      {
+        // every dP^T column of this warp is read before any is overwritten
+        uint32_t d[64];
+        tmem_ld32(tB + lane_off + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&d[0]));
+        tmem_ld32(tB + lane_off + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&d[32]));
         tmem_ld_wait();
+        // P^T and dS^T (16-bit) go over the very dP^T columns this warp has just read, so no other
+        // warp has to be waited for: columns [64 half, +32) hold P^T, [64 half + 32, +32) hold dS^T.
+        // They are handed over in two chunks of 32 queries, so that the products of the first chunk
+        // run while the second is still being formed.
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          dpk[c * 16 + (i >> 1)] = pack2<kBf16>(fmaf(pr[c * 32 + i], __uint_as_float(d[i]), npd[c * 32 + i]),
-                                                fmaf(pr[c * 32 + i + 1], __uint_as_float(d[i + 1]), npd[c * 32 + i + 1]));
+        for (int ch = 0; ch < 2; ++ch) {
+          uint32_t pp[16], dd[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int e = ch * 32 + i;
+            pp[i >> 1] = ppk[e >> 1];
+            dd[i >> 1] = pack2<kBf16>(fmaf(pr[e], __uint_as_float(d[e]), npd[e]),
+                                      fmaf(pr[e + 1], __uint_as_float(d[e + 1]), npd[e + 1]));
+          }
+          tmem_st16(tB + lane_off + half * 64 + ch * 16, pp);
+          tmem_st16(tB + lane_off + half * 64 + 32 + ch * 16, dd);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->pds_ready[ch]);
         }
       }
-      // P^T and dS^T (16-bit) go over the very dP^T columns this warp has just read, so no other
-      // warp has to be waited for: columns [64 half, +32) hold P^T, [64 half + 32, +32) hold dS^T
-      tmem_st32(tB + lane_off + half * 64, ppk);
-      tmem_st32(tB + lane_off + half * 64 + 32, dpk);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->pds_ready);
+      RSWA_TRC(bwd, warp == 4 && lane == 0 && it < 32, it * 32 + 3);
     }
 
     // epilogue: dK (scaled) and dV for this key tile
+    RSWA_TRC(bwd, warp == 4 && lane == 0, 1922);
     if (ok && n_iter > 0) ok = mbar_wait(&ctl->done, 0, err, kErrWaitEpilogue);
+    RSWA_TRC(bwd, warp == 4 && lane == 0, 1923);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
     if (ok && ctl->err == 0) {
@@ -456,6 +472,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     }
   }
 
+  RSWA_TRC(bwd, warp == 4 && lane == 0, 1924);
   // no product waited for K and V: their copy must still have landed before the CTA goes away
   if (threadIdx.x == 0 && n_iter == 0) mbar_wait<200>(&ctl->kv_full, 0, err, kErrWaitProducer);
   tc_fence_before();
@@ -464,6 +481,7 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int total_tiles) {
     tc_fence_after();
     tmem_dealloc(tmem, kBwdTmemCols);
   }
+  RSWA_TRC(bwd, threadIdx.x == 0, 1925);
   if (threadIdx.x == 0 && ctl->err != 0) atomicCAS(p.status, 0, ctl->err);
 }
 

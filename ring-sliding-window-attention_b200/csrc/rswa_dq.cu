@@ -193,7 +193,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         }
         if (ok) mbar_arrive(&ctl->geom_free[slot]);
       }
-    } else if (warp == 1) {
+    } else if (warp == 1 && elect_one()) {
       // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T
       constexpr uint32_t id_kk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t kTile16 = kTileBytes >> 4;
@@ -203,34 +203,34 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       int n = 0, kc = 0, ic = 0;  // kc: key tiles of earlier items = running index of this item's tile 0
       for (;; ++n) {
         const int slot = n & 1;
-        ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
+        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
         if (!ok || ctl->item[slot] < 0) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
-          ok = mbar_wait_w<kMmaPollNs>(&ctl->q_full, ic & 1, err, kErrWaitMma);
+          ok = mbar_wait<kMmaPollNs>(&ctl->q_full, ic & 1, err, kErrWaitMma);
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
             const int sk = g % kDqKStages;
-            ok = mbar_wait_w<kMmaPollNs>(&ctl->k_full[sk], (g / kDqKStages) & 1, err, kErrWaitMma);
+            ok = mbar_wait<kMmaPollNs>(&ctl->k_full[sk], (g / kDqKStages) & 1, err, kErrWaitMma);
             // S buffer g & 1 last held dS of tile g - 2: the dQ product that reads it must be complete
-            if (ok && g >= 2) ok = mbar_wait_w<kMmaPollNs>(&ctl->s_free[g & 1], ((g >> 1) - 1) & 1, err, kErrWaitMma);
+            if (ok && g >= 2) ok = mbar_wait<kMmaPollNs>(&ctl->s_free[g & 1], ((g >> 1) - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
             tc_fence_after();
             const uint64_t dKs = dKk + sk * kTile16;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-              mma_ss_w(tmem + 128 * (g & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
+              mma_ss(tmem + 128 * (g & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
             }
-            mma_commit_w(&ctl->s_ready[g & 1]);
-            if (j + 1 == n_tiles) mma_commit_w(&ctl->q_free);  // that was the item's last read of Q
+            mma_commit(&ctl->s_ready[g & 1]);
+            if (j + 1 == n_tiles) mma_commit(&ctl->q_free);  // that was the item's last read of Q
           }
           kc += n_tiles;
           ++ic;
         }
-        if (ok && lane == 0) mbar_arrive(&ctl->geom_free[slot]);
+        if (ok) mbar_arrive(&ctl->geom_free[slot]);
       }
-    } else if (warp == 3) {
+    } else if (warp == 3 && elect_one()) {
       // ------------------------------------------------------------------ MMA issuer 3: dQ += dS K
       constexpr uint32_t id_tn = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 1);
       constexpr uint32_t kTile16 = kTileBytes >> 4;
@@ -239,33 +239,33 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       int n = 0, kc = 0, ic = 0;
       for (;; ++n) {
         const int slot = n & 1;
-        ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
+        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
         if (!ok || ctl->item[slot] < 0) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
-            ok = mbar_wait_w<kMmaPollNs>(&ctl->ds_ready, g & 1, err, kErrWaitMma);
+            ok = mbar_wait<kMmaPollNs>(&ctl->ds_ready, g & 1, err, kErrWaitMma);
             // the first product of an item overwrites dQ: the previous item's must have been read out
-            if (ok && j == 0 && ic > 0) ok = mbar_wait_w<kMmaPollNs>(&ctl->dq_drained, (ic - 1) & 1, err, kErrWaitMma);
+            if (ok && j == 0 && ic > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dq_drained, (ic - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
             tc_fence_after();
             const uint64_t dKj = dKm + (g % kDqKStages) * kTile16;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              mma_ts_w(tDQ, tmem + 128 * (g & 1) + (k >> 1) * 32 + (k & 1) * 8, dKj + k * 128, id_tn,
+              mma_ts(tDQ, tmem + 128 * (g & 1) + (k >> 1) * 32 + (k & 1) * 8, dKj + k * 128, id_tn,
                      (j > 0 || k > 0) ? 1u : 0u);
             }
-            mma_commit_w(&ctl->k_free[g % kDqKStages]);
-            mma_commit_w(&ctl->s_free[g & 1]);
+            mma_commit(&ctl->k_free[g % kDqKStages]);
+            mma_commit(&ctl->s_free[g & 1]);
           }
-          if (ok) mma_commit_w(&ctl->done);
+          if (ok) mma_commit(&ctl->done);
           kc += n_tiles;
           ++ic;
         }
-        if (ok && lane == 0) mbar_arrive(&ctl->geom_free[slot]);
+        if (ok) mbar_arrive(&ctl->geom_free[slot]);
       }
-    } else if (warp == 2) {
+    } else if (warp == 2 && elect_one()) {
       // ------------------------------------------------------------------ MMA issuer 2: dP
       constexpr uint32_t id_kk = idesc_f16(128, 128, kBf16 ? 1 : 0, 0, 0);
       constexpr uint32_t kTile16 = kTileBytes >> 4;
@@ -275,33 +275,33 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       int n = 0, kc = 0, ic = 0;
       for (;; ++n) {
         const int slot = n & 1;
-        ok = mbar_wait_w<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
+        ok = mbar_wait<kMmaPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitMma);
         if (!ok || ctl->item[slot] < 0) break;
         const int n_tiles = ctl->geom[slot].n_tiles;
         if (n_tiles > 0) {
-          ok = mbar_wait_w<kMmaPollNs>(&ctl->do_full, ic & 1, err, kErrWaitMma);
+          ok = mbar_wait<kMmaPollNs>(&ctl->do_full, ic & 1, err, kErrWaitMma);
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
             const int sv = g & 1;
-            ok = mbar_wait_w<kMmaPollNs>(&ctl->v_full[sv], (g >> 1) & 1, err, kErrWaitMma);
+            ok = mbar_wait<kMmaPollNs>(&ctl->v_full[sv], (g >> 1) & 1, err, kErrWaitMma);
             // the compute warps must have read dP of the previous tile out of TMEM
-            if (ok && g > 0) ok = mbar_wait_w<kMmaPollNs>(&ctl->dp_loaded, (g - 1) & 1, err, kErrWaitMma);
+            if (ok && g > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dp_loaded, (g - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
             tc_fence_after();
             const uint64_t dVs = dVk + sv * kTile16;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
               const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-              mma_ss_w(tDP, dDO + off, dVs + off, id_kk, k > 0 ? 1u : 0u);
+              mma_ss(tDP, dDO + off, dVs + off, id_kk, k > 0 ? 1u : 0u);
             }
-            mma_commit_w(&ctl->dp_ready);
-            mma_commit_w(&ctl->v_free[sv]);
+            mma_commit(&ctl->dp_ready);
+            mma_commit(&ctl->v_free[sv]);
           }
-          if (ok) mma_commit_w(&ctl->do_free);
+          if (ok) mma_commit(&ctl->do_free);
           kc += n_tiles;
           ++ic;
         }
-        if (ok && lane == 0) mbar_arrive(&ctl->geom_free[slot]);
+        if (ok) mbar_arrive(&ctl->geom_free[slot]);
       }
     }
   } else {
