@@ -34,8 +34,10 @@ extern "C" {
 #define RSWA_E_CUDA (-3)     /* a CUDA runtime/driver call failed at launch time */
 #define RSWA_E_NOALLOC_SIZE (-4) /* rswa_bwd_noalloc: the problem does not fit the built-in scratch */
 
-/* size of the scratch array inside the library that rswa_bwd_noalloc works in */
-#define RSWA_NOALLOC_SCRATCH_BYTES (64ll << 20)
+/* size of the scratch array inside the library that rswa_bwd_noalloc works in: 64 MiB for the two
+ * float rows per (batch row, head, token) plus the 256 bytes of work counters every backward
+ * workspace ends with */
+#define RSWA_NOALLOC_SCRATCH_BYTES ((64ll << 20) + 256)
 
 /* bits of rswa_bwd_params_t.flags */
 #define RSWA_BWD_INIT 1   /* fill the workspace rows: delta = rowsum(dO*O) and lse*log2(e) */
@@ -143,8 +145,8 @@ int rswa_bwd(const rswa_bwd_params_t* p, void* stream);
  * that gave away all device memory at start-up, or that must not stall their other streams with
  * the device-wide synchronisation an allocation implies.
  *  - rswa_bwd_workspace_bytes(batch, q_len, n_q_heads, 128) must not exceed
- *    RSWA_NOALLOC_SCRATCH_BYTES (batch*n_q_heads*q_len <= about 8 million rows, e.g. 262144 tokens of
- *    32 heads); larger problems return RSWA_E_NOALLOC_SIZE and launch nothing.
+ *    RSWA_NOALLOC_SCRATCH_BYTES (batch * n_q_heads * q_len padded to whole tiles <= 8388608 rows:
+ *    262144 tokens of 32 heads just fit); larger problems return RSWA_E_NOALLOC_SIZE and launch nothing.
  *  - The first call on each device looks the array's device address up (with that device
  *    current).  Make that first call outside any stream capture.
  *  - All calls on a device share the array: it is rewritten at the start of each call, and

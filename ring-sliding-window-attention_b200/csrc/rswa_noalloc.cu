@@ -10,7 +10,7 @@
 // other streams of the process.  For them the scratch lives in a fixed array in this library's
 // device image; the caller passes inputs and outputs only.
 //
-// The price: the array has a fixed size (RSWA_NOALLOC_SCRATCH_BYTES, 64 MiB) that every GPU which
+// The price: the array has a fixed size (RSWA_NOALLOC_SCRATCH_BYTES, 64 MiB + 256 bytes) that every GPU which
 // loads the library holds until the process exits, problems that need more are rejected, and all
 // calls share the one array, so two calls that may overlap on the GPU (different streams) race.
 #include <mutex>
@@ -31,9 +31,14 @@ void* g_scratch_addr[kMaxDevices] = {nullptr};
 int scratch_for_current_device(void** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+  if (e != cudaSuccess) {
     rswa::set_error("rswa_bwd_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
     return RSWA_E_CUDA;
+  }
+  if (dev < 0 || dev >= kMaxDevices) {
+    rswa::set_error("rswa_bwd_noalloc: device index %d is outside the %d devices this entry point keeps a scratch address for",
+                    dev, kMaxDevices);
+    return RSWA_E_UNSUPPORTED;
   }
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (g_scratch_addr[dev] == nullptr) {
@@ -67,13 +72,16 @@ extern "C" int rswa_bwd_noalloc(const rswa_bwd_params_t* p, void* stream) {
   if (need > RSWA_NOALLOC_SCRATCH_BYTES) {
     rswa::set_error(
         "rswa_bwd_noalloc: this problem needs %lld bytes of scratch, the built-in array holds %lld "
-        "(batch * n_q_heads * q_len must stay below about %lld); use rswa_bwd with a caller-owned workspace",
+        "(batch * n_q_heads * q_len, padded to whole tiles, may be %lld at most); use rswa_bwd with a caller-owned workspace",
         static_cast<long long>(need), static_cast<long long>(RSWA_NOALLOC_SCRATCH_BYTES),
-        static_cast<long long>(RSWA_NOALLOC_SCRATCH_BYTES / 8));
+        static_cast<long long>((RSWA_NOALLOC_SCRATCH_BYTES - 256) / 8));
     return RSWA_E_NOALLOC_SIZE;
   }
+  // the remaining argument checks come before the array is looked up: a rejected call touches nothing
+  int rc = rswa::check_geom(p->g, false);
+  if (rc) return rc;
   void* scratch = nullptr;
-  int rc = scratch_for_current_device(&scratch);
+  rc = scratch_for_current_device(&scratch);
   if (rc) return rc;
   // Same work as rswa_bwd over the built-in scratch.  A whole backward in one call: INIT rewrites the
   // delta and scaled-lse rows (the array still holds the previous call's), FINISH produces dq.

@@ -43,9 +43,17 @@ bwd_main_events = None
 fwd_events = None
 
 
+def _dev_key(device: torch.device):
+    """('cuda', index) with a bare "cuda" resolved to the current device, so that every spelling of a
+    device names the same status word."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return (device.type, index)
+
+
 def status_word(device: torch.device) -> torch.Tensor:
     """Device word the kernels raise when a bounded device-side wait runs out."""
-    key = (device.type, device.index)
+    key = _dev_key(device)
+    device = torch.device(*key)
     if key not in _status:
         _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[key]
@@ -75,7 +83,7 @@ _mirrors = {}
 
 
 def _mirror(device: torch.device) -> _StatusMirror:
-    key = (device.type, device.index)
+    key = _dev_key(device)
     if key not in _mirrors:
         _mirrors[key] = _StatusMirror(device)
     return _mirrors[key]
@@ -99,7 +107,7 @@ def mirror_status(device: torch.device) -> None:
 def raise_if_reported(device: torch.device, wait: bool = False) -> None:
     """Raises RuntimeError if the last mirrored status word was non-zero, and clears the word so that
     the following call runs normally.  Without `wait` a copy still in flight is left for later."""
-    m = _mirrors.get((device.type, device.index))
+    m = _mirrors.get(_dev_key(device))
     if m is None or not m.pending or torch.cuda.is_current_stream_capturing():
         return
     if wait:
@@ -276,7 +284,7 @@ def bwd_noalloc(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse
 
     For integrations that may not allocate device memory where they call the backward (they only
     hold the operator's own tensors, or allocation is forbidden after start-up): the scratch is
-    the fixed 64 MiB array inside librswa.so.  Raises ValueError when the problem is too large
+    the fixed array (64 MiB + 256 bytes) inside librswa.so.  Raises ValueError when the problem is too large
     for it.  Calls on one device share that array, so they must not overlap on the GPU.
     """
     for name, t in (("q", q), ("out", out), ("dout", dout), ("dq", dq)):

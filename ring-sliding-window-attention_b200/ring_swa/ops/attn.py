@@ -4,11 +4,14 @@ Each forward function computes one partial result over the given keys and folds 
 caller's running (global_attn_out, global_softmax_lse); each backward function writes dq and the
 stacked dkv for the same keys from the final out / lse.  kv and dkv are stacked [2, B, S, Hkv, D].
 
-A windowed, non-causal call with more queries than keys keeps the reference's meaning
-(ring_swa/ops/attn.py:38-60, 93-126): the leading q_len - kv_len queries see every key, the trailing
-kv_len queries see the window; these are two launches on disjoint query rows, and dkv is the
-float32 sum of the two parts.  Sliced lse views are passed as they are (the kernels take a batch
-and a head stride), so the reference's defensive .clone() calls have no counterpart.
+A call with more queries than keys keeps the reference's meaning unless it is plain full attention
+(ring_swa/ops/attn.py:21, 38-60, 93-126; the same predicate, `causal` included): the leading
+q_len - kv_len queries see every key, the trailing kv_len queries see the window, both parts with
+causal=False; these are two launches on disjoint query rows, and dkv is the float32 sum of the two
+parts.  The backward differentiates exactly that (the reference hands `causal` on to the parts of its
+backward, which for causal=True is not the gradient of its own forward; its callers only take this
+path with causal=False).  Sliced lse views are passed as they are (the kernels take a batch and a
+head stride), so the reference's defensive .clone() calls have no counterpart.
 """
 from typing import Tuple
 
@@ -25,7 +28,7 @@ from .wrap_flash import (
 
 def flash_attn_fwd_func(q: torch.Tensor, kv: torch.Tensor, softmax_scale: float, window_size: Tuple[int, int],
                         causal: bool, global_attn_out: torch.Tensor, global_softmax_lse: torch.Tensor) -> None:
-    if q.shape[1] > kv.shape[2] and not causal and tuple(window_size) != (-1, -1):
+    if not (q.shape[1] <= kv.shape[2] or (not causal and tuple(window_size) == (-1, -1))):
         kv_len = kv.shape[2]
         flash_attn_fwd_func(q[:, :-kv_len], kv, softmax_scale, (-1, -1), False,
                             global_attn_out[:, :-kv_len], global_softmax_lse[:, :, :-kv_len])
@@ -40,15 +43,15 @@ def flash_attn_fwd_func(q: torch.Tensor, kv: torch.Tensor, softmax_scale: float,
 def flash_attn_bwd_func(q: torch.Tensor, kv: torch.Tensor, o: torch.Tensor, softmax_lse: torch.Tensor,
                         do: torch.Tensor, dq: torch.Tensor, dkv: torch.Tensor, softmax_scale: float,
                         window_size: Tuple[int, int], causal: bool) -> None:
-    if q.shape[1] > kv.shape[2] and not causal and tuple(window_size) != (-1, -1):
+    if not (q.shape[1] <= kv.shape[2] or (not causal and tuple(window_size) == (-1, -1))):
         kv_len = kv.shape[2]
         acc = torch.zeros_like(dkv, dtype=torch.float32)
         part = torch.empty_like(acc)
         flash_attn_bwd_func(q[:, :-kv_len], kv, o[:, :-kv_len], softmax_lse[:, :, :-kv_len], do[:, :-kv_len],
-                            dq[:, :-kv_len], part, softmax_scale, (-1, -1), causal)
+                            dq[:, :-kv_len], part, softmax_scale, (-1, -1), False)
         acc.add_(part)
         flash_attn_bwd_func(q[:, -kv_len:], kv, o[:, -kv_len:], softmax_lse[:, :, -kv_len:], do[:, -kv_len:],
-                            dq[:, -kv_len:], part, softmax_scale, window_size, causal)
+                            dq[:, -kv_len:], part, softmax_scale, window_size, False)
         acc.add_(part)
         dkv.copy_(acc)
         return

@@ -41,7 +41,9 @@ def reduce_sum_tesnsor_to_rank(tensor: torch.Tensor, dst_rank: int, cp_group: Pr
 def exchange_and_sum_tensors(tensor_to_send: torch.Tensor, send_to_rank: int, cp_group: ProcessGroup) -> torch.Tensor:
     """Every rank sends one tensor to one group rank; returns the sum of what this rank received
     (ring_swa/ops/comm.py:102-149).  Built on all_gather so that it also runs on backends without
-    all_to_all."""
+    all_to_all.  Cost: two all_gathers (the destinations, then every rank's tensor: world_size times the
+    bytes of the reference's single all_to_all, which moves one tensor per rank pair) and a local sum;
+    meant for the few hundred bytes of sink gradients the reference uses it for, not for bulk data."""
     ws = dist.get_world_size(group=cp_group)
     me = dist.get_rank(group=cp_group)
     dst = torch.tensor([int(send_to_rank)], dtype=torch.long, device=tensor_to_send.device)

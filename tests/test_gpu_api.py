@@ -63,6 +63,30 @@ def test_varlen_functions():
             assert_close(n, a, b)
 
 
+def test_device_side_timeout_reaches_the_host_and_clears():
+    """A bounded device-side wait that runs out raises the status word; kernels launched after that do no
+    work, so the host has to hear of it: the word is mirrored to pinned memory behind every backward and
+    looked at when the next call starts.  The word is set from the host here (nothing on the device
+    faults or waits)."""
+    import ring_swa
+    from ring_swa import _kernels as K
+    dev = torch.device("cuda")
+    q, k, v, do = (randn_bf16(1, 300, h, D, seed=s) for h, s in ((4, 61), (2, 62), (2, 63), (4, 64)))
+    ro, _, rdq, rdk, rdv = dense_attn_fwd_bwd(q, k, v, do, 100)
+    out, dq, dk, dv = _run(ring_swa.ring_sliding_window_attn, q, k, v, do, window_size=100)
+    assert_close("out", out, ro)
+    K.status_word(dev).fill_(103)                      # what a kernel whose wait ran out would leave behind
+    ql, kl, vl = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+    ring_swa.ring_sliding_window_attn(ql, kl, vl, 100).backward(do.to(dev))   # kernels return at once
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="bounded device-side wait"):
+        ring_swa.ring_sliding_window_attn(ql, kl, vl, 100)
+    # the report cleared the word: the next call computes again
+    out, dq, dk, dv = _run(ring_swa.ring_sliding_window_attn, q, k, v, do, window_size=100)
+    for n, a, b in (("out", out, ro), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        assert_close(n, a, b)
+
+
 def test_reference_error_behaviour():
     import ring_swa
     dev = "cuda"
@@ -129,7 +153,7 @@ def _torch_block_reference(q, k, v, do, W, n_sink, a, b, heads):
 
 
 def test_full_size_config_spot_blocks():
-    """BASELINE configuration 2 at full size on one GPU (B=2, S=32768, 32/32 heads, W=1000): blocks of
+    """The headline configuration of the benchmark set at full size on one GPU (B=2, S=32768, 32/32 heads, W=1000): blocks of
     the result are compared with an fp32 torch computation of the same tokens, plus run-to-run
     agreement of the forward."""
     import ring_swa
@@ -188,8 +212,8 @@ def _region_reference(q, k, v, do, W, n_sink, cu, a, b, q_heads):
 
 @pytest.mark.parametrize("name", ["cfg3", "cfg4"])
 def test_full_size_varlen_and_sink_spot_blocks(name):
-    """BASELINE configurations 3 (packed sequences, 32/8 heads, W=4096, 65536 tokens) and 4 (sink + window,
-    32/8 heads, W=8192, 131072 tokens) at full size on one GPU: blocks of out, dq, dk, dv against fp32 torch
+    """The packed configuration (7 sequences, 32/8 heads, W=4096, 65536 tokens) and the sink + window one
+    (32/8 heads, W=8192, 131072 tokens) of the benchmark set at full size on one GPU: blocks of out, dq, dk, dv against fp32 torch
     on the same tokens; the backward is deterministic, so a second run must agree bit for bit."""
     import ring_swa
     dev = torch.device("cuda")
@@ -234,4 +258,83 @@ def test_full_size_varlen_and_sink_spot_blocks(name):
         sl = slice(lo_k - a, b - a)
         assert_close(f"dk[{lo_k}:{b}]", dk[:, lo_k:b, kh][:, :, 0], rdk[:, sl])
         assert_close(f"dv[{lo_k}:{b}]", dv[:, lo_k:b, kh][:, :, 0], rdv[:, sl])
+        torch.cuda.empty_cache()
+
+
+def _chunked_block_reference(q, k, v, do, W, a, b, kh, q_chunk=2048):
+    """fp32 torch reference, on the GPU, for plain sliding-window attention at sizes where the scores of a
+    whole block's window no longer fit at once: out, lse, dq of queries [a, b) and dk, dv of keys [a, b) of
+    KV head kh (summed over its query heads), from explicit formulas, query chunk by query chunk.  Every
+    query that sees a key of [a, b) -- positions [a, b + W] -- is walked with its complete window."""
+    T, Hq, Hkv = q.shape[1], q.shape[2], k.shape[2]
+    g = Hq // Hkv
+    heads = list(range(kh * g, kh * g + g))
+    scale = D ** -0.5
+    dk = torch.zeros(b - a, D, dtype=torch.float32, device=q.device)
+    dv = torch.zeros_like(dk)
+    out_b = lse_b = dq_b = None
+    hi = min(T, b + W + 1)
+    for c0 in range(a, hi, q_chunk):
+        c1 = min(hi, c0 + q_chunk)
+        k0 = max(0, c0 - W)
+        qs = q[0, c0:c1, heads].float()                      # [n, g, D]
+        dos = do[0, c0:c1, heads].float()
+        ks, vs = k[0, k0:c1, kh].float(), v[0, k0:c1, kh].float()   # [m, D]
+        pq = torch.arange(c0, c1, device=q.device)[:, None]
+        pk = torch.arange(k0, c1, device=q.device)[None, :]
+        mask = (pk <= pq) & (pq - pk <= W)
+        s = torch.einsum("nhd,md->hnm", qs, ks) * scale
+        s = s.masked_fill(~mask[None], float("-inf"))
+        lse = torch.logsumexp(s, -1)                         # [g, n]
+        p = torch.exp(s - lse[..., None])
+        o = torch.einsum("hnm,md->nhd", p, vs)
+        delta = (o * dos).sum(-1).transpose(0, 1)            # [g, n]
+        dp = torch.einsum("nhd,md->hnm", dos, vs)
+        ds = p * (dp - delta[..., None])
+        if c0 == a:                                          # the block's own queries are the chunk's first rows
+            n = b - a
+            out_b, lse_b = o[:n], lse[:, :n]
+            dq_b = torch.einsum("hnm,md->nhd", ds[:, :n], ks) * scale
+        lo_k, hi_k = max(a, k0), min(b, c1)                  # keys of [a, b) this chunk holds
+        if lo_k < hi_k:
+            sl = slice(lo_k - k0, hi_k - k0)
+            dv[lo_k - a:hi_k - a] += torch.einsum("hnm,nhd->md", p[:, :, sl], dos)
+            dk[lo_k - a:hi_k - a] += torch.einsum("hnm,nhd->md", ds[:, :, sl], qs) * scale
+        del s, p, dp, ds
+    return out_b, lse_b, dq_b, dk, dv, heads
+
+
+@pytest.mark.timeout(900)
+def test_full_size_long_window_spot_blocks():
+    """The multi-hop configuration of the benchmark set at full size on one GPU (B=1, S=262144, 64/8 heads,
+    W=65536): a query tile there accumulates over up to 513 key tiles and a key tile's gradients over 8 heads
+    times 513 query tiles.  Blocks of out, dq, dk, dv against fp32 torch on the same tokens, and run-to-run
+    bit equality."""
+    import ring_swa
+    dev = torch.device("cuda")
+    T, Hq, Hkv, W = 262144, 64, 8, 65536
+    g = torch.Generator(device=dev).manual_seed(4)
+    q, k, v, do = (torch.randn(1, T, h, D, device=dev, generator=g).bfloat16() for h in (Hq, Hkv, Hkv, Hq))
+
+    def run():
+        qq, kk, vv = (t.detach().clone().requires_grad_(True) for t in (q, k, v))
+        out = ring_swa.ring_sliding_window_attn(qq, kk, vv, W)
+        out.backward(do)
+        return out.detach(), qq.grad, kk.grad, vv.grad
+
+    got = run()
+    again = run()
+    from ring_swa._kernels import check_device_status
+    check_device_status()
+    for x, y in zip(got, again):
+        assert torch.equal(x, y)
+    del again
+    out, dq, dk, dv = got
+    for a, kh in ((0, 0), (131072 - 64, 3), (T - 128, 7)):
+        b = a + 128
+        ro, _rl, rdq, rdk, rdv, heads = _chunked_block_reference(q, k, v, do, W, a, b, kh)
+        assert_close(f"out[{a}:{b}]", out[0, a:b, heads], ro)
+        assert_close(f"dq[{a}:{b}]", dq[0, a:b, heads], rdq)
+        assert_close(f"dk[{a}:{b}]", dk[0, a:b, kh], rdk)
+        assert_close(f"dv[{a}:{b}]", dv[0, a:b, kh], rdv)
         torch.cuda.empty_cache()

@@ -161,12 +161,12 @@ def test_flash_attn_funcs_accumulate_like_the_reference_loop():
     assert_close("dv", torch.cat([dkv_prev[1], dkv_own[1]], 1), rdv)
 
 
-def test_flash_attn_funcs_more_queries_than_keys():
-    """q_len > kv_len, windowed, not causal: leading queries see every key, trailing ones the window
-    (ring_swa/ops/attn.py:38-60)."""
+@pytest.mark.parametrize("window,causal", [((40, 88), False), ((40, 88), True), ((-1, -1), True), ((-1, 30), False)])
+def test_flash_attn_funcs_more_queries_than_keys(window, causal):
+    """q_len > kv_len and not plain full attention: leading queries see every key, trailing ones the
+    window, both parts with causal=False whatever the caller passed (ring_swa/ops/attn.py:21, 38-60)."""
     from ring_swa.ops import flash_attn_bwd_func, flash_attn_fwd_func
     B, Sq, Sk, H = 1, 300, 128, 2
-    window = (40, 88)
     dev = _dev()
     q, do = randn_bf16(B, Sq, H, D, seed=41), randn_bf16(B, Sq, H, D, seed=44)
     kv = torch.stack([randn_bf16(B, Sk, H, D, seed=42), randn_bf16(B, Sk, H, D, seed=43)])
@@ -178,11 +178,63 @@ def test_flash_attn_funcs_more_queries_than_keys():
     acc = torch.zeros(B, Sq, H, D, dtype=torch.float32, device=dev)
     lse = torch.full((B, H, Sq), float("-inf"), dtype=torch.float32, device=dev)
     qd, dod, kvd = q.to(dev), do.to(dev), kv.to(dev)
-    flash_attn_fwd_func(qd, kvd, SCALE, window, False, acc, lse)
+    flash_attn_fwd_func(qd, kvd, SCALE, window, causal, acc, lse)
     assert_close("out", acc, ro.detach())
     assert_lse_close(lse, rl.detach())
     dq, dkv = torch.empty_like(qd), torch.empty_like(kvd)
-    flash_attn_bwd_func(qd, kvd, acc.to(torch.bfloat16), lse, dod, dq, dkv, SCALE, window, False)
+    flash_attn_bwd_func(qd, kvd, acc.to(torch.bfloat16), lse, dod, dq, dkv, SCALE, window, causal)
     assert_close("dq", dq, qf.grad)
     assert_close("dk", dkv[0], kf.grad)
     assert_close("dv", dkv[1], vf.grad)
+
+
+def test_flash_attn_varlen_funcs_accumulate_and_differentiate():
+    """flash_attn_varlen_fwd_func folds a packed partial result into the caller's accumulators (leading
+    batch of 1, float32 output / float64 lse as the reference's ring keeps them), flash_attn_varlen_bwd_func
+    writes dq and the stacked dkv (ring_swa/ops/attn.py:129-196): the diagonal call over shared boundaries
+    and the rectangular off-diagonal call, merged, equal attention over both key blocks."""
+    from ring_swa.ops import flash_attn_varlen_bwd_func, flash_attn_varlen_fwd_func
+    Hq, Hkv, W = 4, 2, 48
+    lens = [70, 1, 129]
+    cu = [0]
+    for L in lens:
+        cu.append(cu[-1] + L)
+    T = cu[-1]
+    dev = _dev()
+    q, do = randn_bf16(1, T, Hq, D, seed=51), randn_bf16(1, T, Hq, D, seed=54)
+    kv = torch.stack([randn_bf16(1, T, Hkv, D, seed=52), randn_bf16(1, T, Hkv, D, seed=53)])
+    window, causal = (W, 0), True
+    ro, rl, rdq, rdk, rdv = _packed_reference(q[0], kv[0, 0], kv[1, 0], do[0], cu, cu, window, causal)
+    cud = torch.tensor(cu, dtype=torch.int32, device=dev)
+    acc = torch.zeros(1, T, Hq, D, dtype=torch.float32, device=dev)
+    lse = torch.full((1, Hq, T), float("-inf"), dtype=torch.float64, device=dev)
+    qd, dod, kvd = q.to(dev), do.to(dev), kv.to(dev)
+    flash_attn_varlen_fwd_func(qd, kvd, SCALE, window, cud, cud, max(lens), max(lens), causal, acc, lse)
+    assert_close("out", acc[0], ro)
+    assert_lse_close(lse[0], rl)
+    # a second call accumulates: the same keys again double every weight, out stays, lse grows by log 2
+    flash_attn_varlen_fwd_func(qd, kvd, SCALE, window, cud, cud, max(lens), max(lens), causal, acc, lse)
+    assert_close("out (merged twice)", acc[0], ro)
+    assert_lse_close(lse[0], rl + 0.6931471805599453)
+    dq, dkv = torch.empty_like(qd), torch.empty_like(kvd)
+    flash_attn_varlen_bwd_func(qd, kvd, acc.to(torch.bfloat16), torch.as_tensor(rl, device=dev).float()[None], dod, dq, dkv,
+                               cud, cud, max(lens), max(lens), SCALE, window, causal)
+    assert_close("dq", dq[0], rdq)
+    assert_close("dk", dkv[0, 0], rdk)
+    assert_close("dv", dkv[1, 0], rdv)
+    # different query / key boundaries (the off-diagonal hop of the packed ring): one launch per sequence
+    cu_k = [0, 40, 41, 100]
+    kv2 = torch.stack([randn_bf16(1, 100, Hkv, D, seed=55), randn_bf16(1, 100, Hkv, D, seed=56)])
+    ro2, rl2, rdq2, rdk2, rdv2 = _packed_reference(q[0], kv2[0, 0], kv2[1, 0], do[0], cu, cu_k, (30, 10), False)
+    ckd = torch.tensor(cu_k, dtype=torch.int32, device=dev)
+    acc2 = torch.zeros_like(acc)
+    lse2 = torch.full((1, Hq, T), float("-inf"), dtype=torch.float32, device=dev)
+    flash_attn_varlen_fwd_func(qd, kv2.to(dev), SCALE, (30, 10), cud, ckd, max(lens), 59, False, acc2, lse2)
+    assert_close("out (rect)", acc2[0], ro2)
+    assert_lse_close(lse2[0], rl2)
+    dq2, dkv2 = torch.empty_like(qd), torch.empty_like(kv2.to(dev))
+    flash_attn_varlen_bwd_func(qd, kv2.to(dev), acc2.to(torch.bfloat16), lse2, dod, dq2, dkv2, cud, ckd, max(lens), 59,
+                               SCALE, (30, 10), False)
+    assert_close("dq (rect)", dq2[0], rdq2)
+    assert_close("dk (rect)", dkv2[0, 0], rdk2)
+    assert_close("dv (rect)", dkv2[1, 0], rdv2)

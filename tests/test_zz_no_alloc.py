@@ -38,6 +38,11 @@ def _both(seed, S, Hq, Hkv, W, n_sink, cu):
     K.check_device_status()
     for name, a, b in zip(("dq", "dk", "dv"), got, ref):
         assert_close(name, a, b.float())
+    # ... and, directly, against the CPU oracle
+    from oracle.dense_attn import dense_attn_fwd_bwd
+    _o, _l, odq, odk, odv = dense_attn_fwd_bwd(q.cpu(), k.cpu(), v.cpu(), do.cpu(), W, D ** -0.5, n_sink, cu)
+    for name, a, b in zip(("dq", "dk", "dv"), got, (odq, odk, odv)):
+        assert_close(name + " vs oracle", a, b)
 
 
 def test_noalloc_backward_matches_twice_in_a_row():
@@ -53,7 +58,7 @@ def test_noalloc_rejects_what_does_not_fit():
     import ctypes
     from ring_swa import _C
     lib = _C.lib()
-    assert lib.rswa_noalloc_scratch_bytes() == 64 << 20
+    assert lib.rswa_noalloc_scratch_bytes() == (64 << 20) + 256
     # geometry whose two fp32 rows per (batch, head, token) exceed the built-in array: rejected on the
     # host before anything is touched or launched, so small stand-in buffers are enough here
     dev = torch.device("cuda")
@@ -68,3 +73,24 @@ def test_noalloc_rejects_what_does_not_fit():
     assert rc == -4 and b"scratch" in lib.rswa_last_error()
     with pytest.raises(ValueError, match="scratch"):
         _C.check(rc, "rswa_bwd_noalloc")
+
+
+def test_noalloc_accepts_the_largest_documented_shape():
+    """262144 tokens of 32 heads need exactly the array: the size check lets the call through.  The head
+    counts do not divide, so the argument check that comes next rejects it before anything is launched
+    (host-side only: the buffers are stand-ins)."""
+    import ctypes
+    from ring_swa import _C
+    lib = _C.lib()
+    assert lib.rswa_bwd_workspace_bytes(1, 262144, 32, D) == lib.rswa_noalloc_scratch_bytes()
+    buf = torch.zeros(1024, dtype=torch.bfloat16, device="cuda")
+    p = _C.BwdParams()
+    p.g.dtype, p.g.head_dim = 0, D
+    p.g.batch, p.g.q_len, p.g.n_q_heads, p.g.n_kv_heads = 1, 262144, 32, 5
+    p.g.window, p.g.softmax_scale = 10, 0.1
+    for name in ("q", "out", "dout", "lse", "dq", "status"):
+        setattr(p, name, buf.data_ptr())
+    rc = lib.rswa_bwd_noalloc(ctypes.byref(p), None)
+    assert rc == -1 and b"divisible" in lib.rswa_last_error()
+    p.g.q_len = 262144 + 1            # one more token: one more tile of rows, too large
+    assert lib.rswa_bwd_noalloc(ctypes.byref(p), None) == -4
