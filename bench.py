@@ -3,15 +3,22 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
 
 A step is one forward + backward of the public API over one batch of synthetic N(0,1) bf16 inputs.
-The default workload is BASELINE configuration 2 (B=2, S=32768, 32 q heads / 32 kv heads, D=128,
-window 1000).  With --gpus N > 1 (launched under torch.distributed.run, one rank per GPU) the
+The default workload is configuration 2 of the benchmark set (B=2, S=32768, 32 q heads / 32 kv heads,
+D=128, window 1000).  With --gpus N > 1 (launched under torch.distributed.run, one rank per GPU) the
 sequence is sharded over the ranks: by default each rank keeps the 1-GPU chunk (S_global = 32768*N,
-"scaling": "weak"); `--scaling strong` keeps S_global = 32768 and splits it.
+"scaling": "weak"); `--scaling strong` keeps S_global = 32768 and splits it.  The other reading is
+measured in the same run, untimed for `value`, and reported beside it: "strong" (S_global = 32768 split
+over the ranks, with rank 0 alone as the one-GPU figure its efficiency refers to) and "weak_small"
+(4096 tokens per rank).
 
 One JSON line is printed by rank 0.  `value` is timed with inputs resident in HBM; `e2e` adds the
 host->device copy of q, k, v, dO from pinned memory and the device->host copy of out, dq, dk, dv every
 step (three streams: one step's copies overlap the neighbouring steps' compute, none is skipped); `roofline` is the dK/dV backward kernel (the longest one) timed with CUDA events on its stream, `roofline_dq`
 and `roofline_fwd` the other two tensor-core kernels;
+`roofline_merge` / `roofline_delta` the two streaming kernels against the measured copy bandwidth;
+`parity_check` runs four small fixed problems (one-pass halo, window longer than a chunk, sink, packed)
+through the public API on the live process group after the timed region and compares every rank's
+out, dq, dk, dv with a dense fp32 torch computation of the global problem;
 `cpu_baseline` is the dense torch CPU restatement of the reference's test oracle on a bounded slice.
 
 `--impl reference` times that CPU restatement alone (the reference's own attention arithmetic lives in
@@ -48,7 +55,7 @@ WORKLOADS = {
     "small": dict(fn="ring_sliding_window_attn", B=1, S=16384, Hq=16, Hkv=16, W=1000, n_sink=0, seed=1),
 }
 # DRAM bytes (read + write) of one dK/dV-kernel launch on cfg2, from an ncu capture of the "small"
-# workload scaled by the number of key tiles (see profiles/); None until measured
+# workload scaled by the number of key tiles; None until measured
 TRAFFIC_DKDV_CFG2 = 3.02e9
 # cpu sample: a slice of the workload small enough for dense S x S attention on host cores
 CPU_SAMPLE = dict(S=4096, H=2)
@@ -82,6 +89,11 @@ def visible_pairs(a: int, b: int, W: int, n_sink: int, seq_starts=None) -> int:
             if b > f:
                 total += b - f
     return total
+
+
+def packed_pairs(seq_lens, W: int, n_sink: int) -> int:
+    """Visible (query, key) pairs of packed sequences, each starting at its own position 0."""
+    return sum(visible_pairs(0, L, W, n_sink) for L in seq_lens)
 
 
 class ClockSampler:
@@ -201,6 +213,111 @@ def workload_config(args, wl, n):
             "seed": wl["seed"], "cp_size": n, "l2": "inputs larger than L2 (no flush needed)"}
 
 
+
+def dense_reference(q, k, v, do, W, n_sink, cu, scale):
+    """Dense fp32 torch attention of the GLOBAL problem on the current device (a checker for small
+    problems): q [B,T,Hq,D], k/v [B,T,Hkv,D]; a query at p sees key t of its own sequence with t <= p and
+    (p - t <= W or t among the sequence's first n_sink tokens).  Returns out, dq, dk, dv."""
+    B, T, Hq, _ = q.shape
+    g = Hq // k.shape[2]
+    qf, kf, vf = (x.detach().float().requires_grad_(True) for x in (q, k, v))
+    pos = torch.arange(T, device=q.device)
+    start = torch.zeros(T, dtype=torch.long, device=q.device)
+    if cu is not None:
+        for a, b in zip(cu[:-1], cu[1:]):
+            start[a:b] = a
+    same = start[:, None] == start[None, :]
+    mask = same & (pos[None, :] <= pos[:, None]) & ((pos[:, None] - pos[None, :] <= W) |
+                                                    (pos[None, :] < start[:, None] + n_sink))
+    s = torch.einsum("bihd,bjhd->bhij", qf, kf.repeat_interleave(g, 2)) * scale
+    s = s.masked_fill(~mask[None, None], float("-inf"))
+    o = torch.einsum("bhij,bjhd->bihd", torch.softmax(s, -1), vf.repeat_interleave(g, 2))
+    o.backward(do.float())
+    return o.detach(), qf.grad, kf.grad, vf.grad
+
+
+def parity_check(ring_swa, dev, group, n, rank):
+    """Four small fixed problems through the public API on the live process group, each rank's slice of
+    out, dq, dk, dv against the dense fp32 computation of the global problem (every rank computes that
+    itself from the same seed).  Returns the worst errors over cases, tensors and ranks."""
+    S = 1024
+    T = S * n
+    cases = [
+        dict(fn="ring_sliding_window_attn", W=300, n_sink=0, cu=None, B=2),      # halo from the previous rank only
+        dict(fn="ring_sliding_window_attn", W=2500, n_sink=0, cu=None, B=1),     # window longer than a chunk: several hops, merged
+        dict(fn="ring_streaming_llm_attn", W=200, n_sink=1, cu=None, B=1),       # sink fetched from rank 0
+        dict(fn="ring_sliding_window_attn_varlen", W=700, n_sink=0, B=1,
+             cu=[0, 300, 301, T // 2 + 77, T - 200, T]),                         # packed, sequences crossing rank edges
+    ]
+    worst_abs, worst_rel, ok = 0.0, 0.0, True
+    for ci, c in enumerate(cases):
+        gen = torch.Generator(device=dev).manual_seed(4242 + ci)           # the same global tensors on every rank
+        Hq, Hkv = 4, 2
+        qg, kg, vg, dg = (torch.randn(c["B"], T, h, D, device=dev, generator=gen).bfloat16() for h in (Hq, Hkv, Hkv, Hq))
+        scale = D ** -0.5
+        ref = dense_reference(qg, kg, vg, dg, c["W"], c["n_sink"], c["cu"], scale)
+        sl = slice(rank * S, (rank + 1) * S)
+        varlen = c["cu"] is not None
+        loc = [x[:, sl].contiguous() for x in (qg, kg, vg, dg)]
+        if varlen:
+            loc = [x[0] for x in loc]
+        ql, kl, vl = (x.detach().requires_grad_(True) for x in loc[:3])
+        kw = dict(window_size=c["W"])
+        if n > 1:
+            kw.update(cp_group=group, cp_size=n, cp_local_rank=rank)
+        if varlen:
+            kw.update(cu_seqlens=torch.tensor(c["cu"], dtype=torch.int32, device=dev), cp_size=n)
+        out = getattr(ring_swa, c["fn"])(ql, kl, vl, **kw)
+        out.backward(loc[3])
+        for got, want in zip((out.detach(), ql.grad, kl.grad, vl.grad), ref):
+            w = want[:, sl] if not varlen else want[0, sl]
+            err = (got.float() - w).abs()
+            worst_abs = max(worst_abs, float(err.max()))
+            worst_rel = max(worst_rel, float((got.float() - w).norm() / w.norm().clamp_min(1e-20)))
+            ok = ok and bool((err <= 2e-2 + 1e-2 * w.abs()).all()) and bool(torch.isfinite(got).all())
+    t = torch.tensor([worst_abs, worst_rel, 0.0 if ok else 1.0], device=dev, dtype=torch.float64)
+    if n > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"max_abs_err": t[0].item(), "rel_l2": t[1].item(), "ok": t[2].item() == 0.0 and t[1].item() <= 1e-2,
+            "cases": len(cases), "tokens_per_rank": S, "tolerance": "abs <= 2e-2 + 1e-2*|ref|, rel L2 <= 1e-2"}
+
+
+def time_streaming_kernels(K, q, do, steps):
+    """CUDA-event times (ms per launch) of the merge kernel and of the delta kernel on tensors of the
+    workload's output shape, and their algorithmic bytes."""
+    dev = q.device
+    B, S, H, _ = q.shape
+    o_a, o_b = q.clone(), do.clone()
+    lse_a = torch.randn(B, H, S, device=dev)
+    lse_b = torch.randn(B, H, S, device=dev)
+    o_c, lse_c = torch.empty_like(o_a), torch.empty_like(lse_a)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    for _ in range(3):
+        K.merge(o_a, lse_a, o_b, lse_b, out=o_c, lse_out=lse_c)
+    ev[0].record()
+    for _ in range(steps):
+        K.merge(o_a, lse_a, o_b, lse_b, out=o_c, lse_out=lse_c)
+    ev[1].record()
+    torch.cuda.synchronize()
+    merge_ms = ev[0].elapsed_time(ev[1]) / steps
+    merge_bytes = B * S * H * (3 * D * 2 + 3 * 4)
+    # the delta kernel alone: an INIT call without K/V gradient buffers launches nothing else
+    from ring_swa import _C
+    ws = K.bwd_workspace(q)
+    kv = q[:, :, :1]
+    span = [K.KVSpan(kv, kv, 0)]
+    for _ in range(3):
+        K.bwd(q, span, o_a, lse_a, do, o_c, 1, 0, 1.0, workspace=ws, flags=_C.BWD_INIT)
+    ev[0].record()
+    for _ in range(steps):
+        K.bwd(q, span, o_a, lse_a, do, o_c, 1, 0, 1.0, workspace=ws, flags=_C.BWD_INIT)
+    ev[1].record()
+    torch.cuda.synchronize()
+    delta_ms = ev[0].elapsed_time(ev[1]) / steps
+    delta_bytes = B * S * H * (2 * D * 2 + 4 + 2 * 4)      # out and dO read once, lse read, two float rows written
+    return merge_ms, merge_bytes, delta_ms, delta_bytes
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -211,6 +328,7 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the strong / weak_small series")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     wl = WORKLOADS[args.workload]
@@ -357,12 +475,57 @@ def main():
         e2e_ms = f0.elapsed_time(f1) / n_e2e
     clocks = sampler.stop() if sampler else None
 
+    # ---------------------------------------------------------------- the other scaling readings (untimed for `value`)
+    def timed_series(S_rank, ranks, kw_run):
+        """ms per step (this rank) of `steps` steps at S_rank tokens per rank, after `warmup` steps."""
+        gg = torch.Generator(device=dev).manual_seed(wl["seed"] * 1000 + 77 + rank)
+        qq, kk, vv, dd = (torch.randn(B, S_rank, h, D, device=dev, generator=gg).bfloat16() for h in (Hq, Hkv, Hkv, Hq))
+
+        def one():
+            qq.requires_grad_(True), kk.requires_grad_(True), vv.requires_grad_(True)
+            fn(qq, kk, vv, **kw_run).backward(dd)
+            qq.grad = kk.grad = vv.grad = None
+
+        for _ in range(args.warmup):
+            one()
+        if ranks > 1:
+            sync_all()
+        else:
+            torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(args.steps):
+            one()
+        a1.record()
+        torch.cuda.synchronize()
+        return a0.elapsed_time(a1) / args.steps
+
+    extra_ms = [0.0, 0.0, 0.0]      # strong at n ranks, rank 0 alone on the whole sequence, weak_small
+    do_extra = not varlen and not args.no_extra and args.scaling == "weak"
+    S_small = 4096
+    if do_extra:
+        if n > 1:
+            extra_ms[0] = timed_series(wl["S"] // n, n, kw)
+            sync_all()
+            if rank == 0:       # the one-GPU time of the same global sequence, the other ranks idle
+                extra_ms[1] = timed_series(wl["S"], 1, dict(window_size=W))
+            sync_all()
+        extra_ms[2] = timed_series(S_small, n, kw)
+        sync_all()
+
+    # ---------------------------------------------------------------- streaming kernels, parity
+    stream_k = time_streaming_kernels(K, q if not varlen else q[None], do if not varlen else do[None], 10) if rank == 0 else None
+    sync_all()
+    parity = parity_check(ring_swa, dev, group, n, rank)
+    sync_all()
+    K.check_device_status(dev)
+
     # ---------------------------------------------------------------- reduce over ranks
-    stats = torch.tensor([ms, fwd_ms, bwd_ms, e2e_ms if not args.no_e2e else 0.0, dq_ms], device=dev,
+    stats = torch.tensor([ms, fwd_ms, bwd_ms, e2e_ms if not args.no_e2e else 0.0, dq_ms] + extra_ms, device=dev,
                          dtype=torch.float64)
     if n > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-    ms, fwd_ms, bwd_ms, e2e_ms, dq_ms = stats.tolist()
+    ms, fwd_ms, bwd_ms, e2e_ms, dq_ms, strong_ms, alone_ms, small_ms = stats.tolist()
 
     if rank == 0:
         tokens = B * S_g
@@ -376,8 +539,7 @@ def main():
                 and clocks["sm_mhz"] < 0.9 * clocks["sm_max_mhz"]:
             peak_tf, peak_name = peak_sustained, "bf16_tflops_sustained (SM clock below 90 % of max under the power cap)"
         if varlen:
-            from oracle.dense_attn import in_window_pairs
-            pairs_total = in_window_pairs(seq_lens, W, n_sink)
+            pairs_total = packed_pairs(seq_lens, W, n_sink)
         else:
             pairs_total = B * visible_pairs(0, S_g, W, n_sink)
         # work is near-uniform over ranks except the first ones; the slowest rank is the last
@@ -408,7 +570,30 @@ def main():
                              "unit": "TFLOP/s", "frac": ach_fwd / peak_tf, "ms_per_launch": fwd_ms},
             "gpu_launches": launches,
             "clocks": clocks,
+            "parity_check": parity,
         }
+        if stream_k is not None:
+            merge_ms, merge_bytes, delta_ms, delta_bytes = stream_k
+            for name, kern, t_ms, nbytes in (("roofline_merge", "merge_kernel", merge_ms, merge_bytes),
+                                            ("roofline_delta", "delta_kernel", delta_ms, delta_bytes)):
+                gbs = nbytes / (t_ms * 1e-3) / 1e9
+                line[name] = {"kernel": kern, "bound": "hbm", "achieved": gbs, "peak": peak_gbs, "unit": "GB/s",
+                              "frac": gbs / peak_gbs, "ms_per_launch": t_ms, "algorithmic_bytes_per_launch": nbytes,
+                              "peak_source": f"{peak_kind} hbm_gbs (copy)"}
+        if do_extra:
+            def scaling_obj(S_glob, t_ms, n_ranks):
+                pr = B * visible_pairs(0, S_glob, W, n_sink)
+                return {"S_global": S_glob, "S_per_gpu": S_glob // n_ranks, "ms_per_step": t_ms,
+                        "tokens_per_s": B * S_glob / (t_ms * 1e-3),
+                        "tflops_per_gpu": 14 * D * Hq * pr / n_ranks / (t_ms * 1e-3) / 1e12}
+            if n > 1:
+                line["strong"] = scaling_obj(wl["S"], strong_ms, n)
+                line["strong"]["one_gpu_ms_per_step"] = alone_ms
+                line["strong"]["efficiency_vs_n1"] = alone_ms / (n * strong_ms)
+            else:
+                line["strong"] = scaling_obj(wl["S"], ms_step, 1)
+                line["strong"]["efficiency_vs_n1"] = 1.0
+            line["weak_small"] = scaling_obj(S_small * n, small_ms, n)
         if not args.no_e2e:
             line["e2e"] = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d * n,
                            "d2h_bytes_per_step": d2h * n, "ms_per_step": e2e_ms}
