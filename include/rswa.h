@@ -208,6 +208,13 @@ int rswa_merge_acc(const rswa_merge_acc_params_t* p, void* stream);
 int rswa_halo_accumulate(float* acc, int64_t acc_stride_b, const void* recv, int64_t recv_stride_b,
                          int32_t recv_dtype, int32_t batch, int64_t elems_per_batch, void* stream);
 
+/* dst (16-bit) = round(acc + recv), acc itself left untouched: the last of the additions above and the
+ * final cast (ring_swa/sliding_window/nonvarlen.py:320-322, 335-337) in one pass over the data.
+ * dst_dtype: RSWA_DTYPE_BF16 or RSWA_DTYPE_FP16; recv_dtype as for rswa_halo_accumulate. */
+int rswa_halo_accumulate_cast(void* dst, int64_t dst_stride_b, int32_t dst_dtype, const float* acc,
+                              int64_t acc_stride_b, const void* recv, int64_t recv_stride_b, int32_t recv_dtype,
+                              int32_t batch, int64_t elems_per_batch, void* stream);
+
 /* dst (16-bit) = src (float), [batch, elems_per_batch] with batch strides: the final cast of
  * ring_swa/sliding_window/nonvarlen.py:335-337. */
 int rswa_cast_from_f32(void* dst, int64_t dst_stride_b, const float* src, int64_t src_stride_b,

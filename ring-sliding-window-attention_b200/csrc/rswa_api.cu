@@ -40,6 +40,28 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 
+// Encoded maps are kept in a small per-thread cache keyed by everything the encoding depends on: a
+// training step presents the same few tensors (same pointers from a caching allocator, same shapes) call
+// after call, and each encoding is a driver call of a microsecond or two, a dozen of them per step and rank.
+namespace {
+struct MapKey {
+  const void* base;
+  int dtype, batch, tokens, heads;
+  long long sb, st, sh;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && dtype == o.dtype && batch == o.batch && tokens == o.tokens && heads == o.heads &&
+           sb == o.sb && st == o.st && sh == o.sh;
+  }
+};
+constexpr int kMapCacheSize = 64;
+struct MapCache {
+  MapKey key[kMapCacheSize];
+  CUtensorMap map[kMapCacheSize];
+  int used = 0, next = 0;
+};
+thread_local MapCache t_map_cache;
+}  // namespace
+
 int make_tile_map(CUtensorMap* map, const void* base, int dtype, int batch, int tokens, int heads,
                   long long sb, long long st, long long sh) {
   EncodeTiledFn enc = get_encode();
@@ -66,6 +88,14 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int batch, int 
     return RSWA_E_ARG;
   }
   if (batch == 1 && sb == 0) sb = static_cast<long long>(tokens) * st;
+  const MapKey key{base, dtype, batch, tokens, heads, sb, st, sh};
+  MapCache& cache = t_map_cache;
+  for (int i = 0; i < cache.used; ++i) {
+    if (cache.key[i] == key) {
+      *map = cache.map[i];
+      return RSWA_OK;
+    }
+  }
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(heads),
                         static_cast<cuuint64_t>(tokens), static_cast<cuuint64_t>(batch)};
   cuuint64_t strides[3] = {static_cast<cuuint64_t>(sh) * 2, static_cast<cuuint64_t>(st) * 2,
@@ -81,6 +111,9 @@ int make_tile_map(CUtensorMap* map, const void* base, int dtype, int batch, int 
               static_cast<int>(r), tokens, heads, sb, st, sh);
     return RSWA_E_CUDA;
   }
+  const int slot = cache.used < kMapCacheSize ? cache.used++ : (cache.next++ % kMapCacheSize);
+  cache.key[slot] = key;
+  cache.map[slot] = *map;
   return RSWA_OK;
 }
 

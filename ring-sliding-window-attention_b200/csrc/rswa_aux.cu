@@ -181,6 +181,30 @@ __global__ void halo_acc_kernel(float* __restrict__ acc, long long acc_sb, const
   *a = x;
 }
 
+// dst = round(acc + recv), nothing written back to acc: the last addition into an accumulator and its
+// final rounding in one pass.  kind of recv as above.
+template <int kKind, bool kBf16>
+__global__ void halo_acc_cast_kernel(uint16_t* __restrict__ dst, long long dst_sb, const float* __restrict__ acc,
+                                     long long acc_sb, const void* __restrict__ recv, long long recv_sb,
+                                     long long vec_per_batch, long long n_vec) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  const long long b = i / vec_per_batch, v = i % vec_per_batch;
+  float4 x = *(reinterpret_cast<const float4*>(acc + b * acc_sb) + v);
+  if constexpr (kKind == 2) {
+    const float4 r = *(reinterpret_cast<const float4*>(static_cast<const float*>(recv) + b * recv_sb) + v);
+    x.x += r.x; x.y += r.y; x.z += r.z; x.w += r.w;
+  } else {
+    const uint2 r = *(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(recv) + b * recv_sb) + v);
+    const float2 r0 = unpack2<kKind == 0>(r.x), r1 = unpack2<kKind == 0>(r.y);
+    x.x += r0.x; x.y += r0.y; x.z += r1.x; x.w += r1.y;
+  }
+  uint2 o;
+  o.x = pack2f<kBf16>(x.x, x.y);
+  o.y = pack2f<kBf16>(x.z, x.w);
+  *(reinterpret_cast<uint2*>(dst + b * dst_sb) + v) = o;
+}
+
 template <bool kBf16>
 __global__ void cast_kernel(uint16_t* __restrict__ dst, long long dst_sb, const float* __restrict__ src,
                             long long src_sb, long long vec_per_batch, long long n_vec) {
@@ -332,4 +356,34 @@ extern "C" int rswa_cast_from_f32(void* dst, int64_t dst_stride_b, const float* 
   if (dtype == 0) cast_kernel<true><<<blocks, threads, 0, s>>>(static_cast<uint16_t*>(dst), dst_stride_b, src, src_stride_b, vpb, n_vec);
   else cast_kernel<false><<<blocks, threads, 0, s>>>(static_cast<uint16_t*>(dst), dst_stride_b, src, src_stride_b, vpb, n_vec);
   return check_launch("rswa_cast_from_f32");
+}
+
+extern "C" int rswa_halo_accumulate_cast(void* dst, int64_t dst_stride_b, int32_t dst_dtype, const float* acc,
+                                         int64_t acc_stride_b, const void* recv, int64_t recv_stride_b,
+                                         int32_t recv_dtype, int32_t batch, int64_t elems_per_batch, void* stream) {
+  if (!dst || !acc || !recv || batch <= 0 || elems_per_batch <= 0 || (elems_per_batch % 4) || (acc_stride_b % 4) ||
+      (recv_stride_b % 4) || (dst_stride_b % 4) || recv_dtype < 0 || recv_dtype > 2 || (dst_dtype != 0 && dst_dtype != 1) ||
+      (reinterpret_cast<uintptr_t>(acc) & 15) || (reinterpret_cast<uintptr_t>(recv) & 15) ||
+      (reinterpret_cast<uintptr_t>(dst) & 7)) {
+    set_error("rswa_halo_accumulate_cast: bad argument (need 16-byte alignment and multiples of 4 elements)");
+    return RSWA_E_ARG;
+  }
+  const long long vpb = elems_per_batch / 4, n_vec = vpb * batch;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((n_vec + threads - 1) / threads);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint16_t* d = static_cast<uint16_t*>(dst);
+#define RSWA_LAUNCH_ACC_CAST(K, B) \
+  halo_acc_cast_kernel<K, B><<<blocks, threads, 0, s>>>(d, dst_stride_b, acc, acc_stride_b, recv, recv_stride_b, vpb, n_vec)
+  if (dst_dtype == 0) {
+    if (recv_dtype == 0) RSWA_LAUNCH_ACC_CAST(0, true);
+    else if (recv_dtype == 1) RSWA_LAUNCH_ACC_CAST(1, true);
+    else RSWA_LAUNCH_ACC_CAST(2, true);
+  } else {
+    if (recv_dtype == 0) RSWA_LAUNCH_ACC_CAST(0, false);
+    else if (recv_dtype == 1) RSWA_LAUNCH_ACC_CAST(1, false);
+    else RSWA_LAUNCH_ACC_CAST(2, false);
+  }
+#undef RSWA_LAUNCH_ACC_CAST
+  return check_launch("rswa_halo_accumulate_cast");
 }

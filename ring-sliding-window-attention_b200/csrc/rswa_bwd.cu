@@ -495,7 +495,14 @@ int launch_bwd(const BwdKernelParams& kp, int dtype, int total_key_tiles, cudaSt
     return RSWA_E_ARG;
   }
   auto kern = dtype == RSWA_DTYPE_BF16 ? rswa_bwd_kernel<true> : rswa_bwd_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmemBytes);
+  // (the attribute is a property of the function on a device: set once per kernel variant and device)
+  static bool attr_set[2][64] = {{false}};
+  int dev_id = 0;
+  cudaError_t e = cudaGetDevice(&dev_id);
+  if (e == cudaSuccess && (dev_id < 0 || dev_id >= 64 || !attr_set[dtype == RSWA_DTYPE_BF16][dev_id])) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmemBytes);
+    if (e == cudaSuccess && dev_id >= 0 && dev_id < 64) attr_set[dtype == RSWA_DTYPE_BF16][dev_id] = true;
+  }
   if (e != cudaSuccess) {
     set_error("rswa_bwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return RSWA_E_CUDA;

@@ -450,7 +450,14 @@ int launch_dq(const BwdKernelParams& kp, int dtype, cudaStream_t stream) {
     return RSWA_E_ARG;
   }
   auto kern = dtype == RSWA_DTYPE_BF16 ? rswa_dq_kernel<true> : rswa_dq_kernel<false>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes);
+  // (the attribute is a property of the function on a device: set once per kernel variant and device)
+  static bool attr_set[2][64] = {{false}};
+  int dev_id = 0;
+  cudaError_t e = cudaGetDevice(&dev_id);
+  if (e == cudaSuccess && (dev_id < 0 || dev_id >= 64 || !attr_set[dtype == RSWA_DTYPE_BF16][dev_id])) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes);
+    if (e == cudaSuccess && dev_id >= 0 && dev_id < 64) attr_set[dtype == RSWA_DTYPE_BF16][dev_id] = true;
+  }
   if (e != cudaSuccess) {
     set_error("rswa_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     return RSWA_E_CUDA;

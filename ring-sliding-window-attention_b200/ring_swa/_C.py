@@ -100,6 +100,8 @@ SYMBOLS = {
     "rswa_merge_acc": (C.c_int, [C.POINTER(MergeAccParams), C.c_void_p]),
     "rswa_halo_accumulate": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                        C.c_int64, C.c_void_p]),
+    "rswa_halo_accumulate_cast": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                            C.c_int32, C.c_int32, C.c_int64, C.c_void_p]),
     "rswa_cast_from_f32": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                      C.c_int64, C.c_void_p]),
     "rswa_event_create": (C.c_void_p, []),

@@ -385,6 +385,20 @@ def halo_accumulate(acc: torch.Tensor, recv: torch.Tensor) -> None:
     launch_count += 1
 
 
+def halo_accumulate_cast(dst: torch.Tensor, acc: torch.Tensor, recv: torch.Tensor) -> None:
+    """dst (16-bit) = round(acc + recv); acc (fp32) is not written.  All [B, ...] with contiguous batch rows."""
+    if acc.dtype != torch.float32 or acc.shape != recv.shape or dst.shape != acc.shape:
+        raise ValueError("halo_accumulate_cast: acc must be float32 and match recv and dst in shape")
+    B, asb, n = _rows(acc)
+    _, rsb, _ = _rows(recv)
+    _, dsb, _ = _rows(dst)
+    code = _C.DTYPE_F32 if recv.dtype == torch.float32 else _dtype_code(recv)
+    _C.check(_C.lib().rswa_halo_accumulate_cast(dst.data_ptr(), dsb, _dtype_code(dst), acc.data_ptr(), asb, recv.data_ptr(),
+                                                rsb, code, B, n, _stream()), "rswa_halo_accumulate_cast")
+    global launch_count
+    launch_count += 1
+
+
 def cast_from_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
     if src.dtype != torch.float32 or dst.shape != src.shape:
         raise ValueError("cast_from_f32: src must be float32 and match dst in shape")

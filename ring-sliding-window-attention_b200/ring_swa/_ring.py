@@ -67,12 +67,9 @@ def _dense(t: torch.Tensor) -> torch.Tensor:
 
 
 def _pack_tail(k4: torch.Tensor, v4: torch.Tensor, length: int) -> torch.Tensor:
-    """[2, B, L, Hkv, D] copy of the trailing `length` tokens of K and V (one message)."""
+    """[2, B, L, Hkv, D] copy of the trailing `length` tokens of K and V (one message, one copy kernel)."""
     S = k4.shape[1]
-    buf = torch.empty((2, k4.shape[0], length) + tuple(k4.shape[2:]), dtype=k4.dtype, device=k4.device)
-    buf[0].copy_(k4[:, S - length:])
-    buf[1].copy_(v4[:, S - length:])
-    return buf
+    return torch.stack((k4[:, S - length:], v4[:, S - length:]))
 
 
 class RingAttn(torch.autograd.Function):
@@ -197,7 +194,9 @@ class RingAttn(torch.autograd.Function):
             recvs.append((s.offset, s.n, g))
         works = _exchange(ops)
 
-        dk4, dv4 = torch.empty_like(k4), torch.empty_like(v4)
+        # dK and dV are one stacked tensor, so that K and V parts go through the helper kernels together
+        dkv = torch.empty((2,) + tuple(k4.shape), dtype=k4.dtype, device=k4.device)
+        dk4, dv4 = dkv[0], dkv[1]
         # Gradients that later ranks return are added in float32 and rounded once.  When they all land
         # on a suffix of the chunk (halo gradients; no sink token inside the chunk), only that suffix is
         # kept in float32: the local K/V go to the kernels as two spans, the body writing its
@@ -220,11 +219,19 @@ class RingAttn(torch.autograd.Function):
         K.bwd(q4, seen + local, out, lse, do4, dq4, workspace=ws, flags=flags, **args)
         _wait(works)
         if acc is not None:
-            for off, n, g in recvs:
-                K.halo_accumulate(acc[0][:, off - acc0:off - acc0 + n], g[0])
-                K.halo_accumulate(acc[1][:, off - acc0:off - acc0 + n], g[1])
-            K.cast_from_f32(dk4[:, acc0:], acc[0])
-            K.cast_from_f32(dv4[:, acc0:], acc[1])
+            # [2, B] is one batch axis for the helper kernels (K and V parts in one launch).  The message
+            # that covers the whole accumulator (the nearest later rank's) goes last: its addition and the
+            # final rounding are one pass.
+            L = S - acc0
+            flat = lambda t: t.reshape((2 * B,) + tuple(t.shape[2:]))  # noqa: E731  (views: [2, B, ...] is contiguous over [2, B])
+            recvs.sort(key=lambda r: r[1])
+            last = recvs[-1] if recvs[-1][0] == acc0 and recvs[-1][1] == L else None
+            for off, n_tok, g in (recvs[:-1] if last is not None else recvs):
+                K.halo_accumulate(flat(acc)[:, off - acc0:off - acc0 + n_tok], flat(g))
+            if last is not None:
+                K.halo_accumulate_cast(flat(dkv)[:, acc0:], flat(acc), flat(last[2]))
+            else:
+                K.cast_from_f32(flat(dkv)[:, acc0:], flat(acc))
         if q4.is_cuda:
             K.mirror_status(q4.device)
         if varlen:

@@ -1,4 +1,5 @@
 """ring_sliding_window_attn_varlen: same signature as ring_swa/sliding_window/varlen.py:362-374."""
+import weakref
 from typing import Optional
 
 import torch
@@ -7,14 +8,33 @@ from torch.distributed import ProcessGroup
 from .._ring import attention, ring_ctx
 
 
+# Host copies of cu_seqlens tensors already seen, by tensor object: a model hands the same tensor to
+# every layer of a step, and only the first of those calls has to wait for the device.  An entry is
+# valid while the very same tensor object is alive and has not been written to since.
+_cu_host_cache = {}
+
+
+def _cu_host(cu_seqlens: torch.Tensor):
+    """(python list of the cumulative lengths, whether the call had to synchronise with the device)."""
+    key = id(cu_seqlens)
+    hit = _cu_host_cache.get(key)
+    if hit is not None and hit[0]() is cu_seqlens and hit[1] == cu_seqlens._version:
+        return hit[2], False
+    host = [int(x) for x in cu_seqlens.tolist()]
+    if len(_cu_host_cache) > 64:
+        _cu_host_cache.clear()
+    _cu_host_cache[key] = (weakref.ref(cu_seqlens), cu_seqlens._version, host)
+    return host, True
+
+
 def _varlen_prologue(q, k, v, cu_seqlens, cp_size):
     assert q.dim() == 3 and k.dim() == 3 and v.dim() == 3, "q, k, v must be [seq_len, heads, head_dim]"
     assert q.shape[0] == k.shape[0] == v.shape[0], "Sequence length must be the same"
     assert q.shape[1] % k.shape[1] == 0, "Number of query heads must be divisible by number of key/value heads"
     # one device-to-host copy, where the reference has its own (and several more further down):
     # the global cumulative lengths drive the halo plan on the host
-    cu_host = [int(x) for x in cu_seqlens.tolist()]
-    if q.is_cuda:
+    cu_host, synced = _cu_host(cu_seqlens)
+    if q.is_cuda and synced:
         # the copy above has synchronised with the device anyway: a good moment to look at the status word
         from .. import _kernels
         _kernels.raise_if_reported(q.device, wait=True)

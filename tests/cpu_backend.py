@@ -96,6 +96,10 @@ def halo_accumulate(acc, recv):
     acc += recv.float()
 
 
+def halo_accumulate_cast(dst, acc, recv):
+    dst.copy_((acc + recv.float()).to(dst.dtype))
+
+
 def cast_from_f32(dst, src):
     dst.copy_(src.to(dst.dtype))
 
@@ -104,3 +108,4 @@ def install():
     import ring_swa._kernels as K
     K.fwd, K.bwd, K.merge = fwd, bwd, merge
     K.bwd_workspace, K.halo_accumulate, K.cast_from_f32 = bwd_workspace, halo_accumulate, cast_from_f32
+    K.halo_accumulate_cast = halo_accumulate_cast
