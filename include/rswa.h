@@ -80,6 +80,7 @@ typedef struct rswa_geom {
 /* Forward: out [batch,q_len,Hq,D] and lse [batch,Hq,q_len] (natural log, fp32; -inf and a zero
  * output row where no key of the given spans is visible).  Only query tiles
  * [q_tile_begin, q_tile_end) are computed (q_tile_end <= 0: all).
+ * With `carry` the call continues a partial result instead of starting a new one.
  * Replaces wrapped_flash_attn_fwd / wrapped_flash_attn_fwd_varlen
  * (ring_swa/ops/wrap_flash.py:168-200, 203-273) and the per-hop mask-case selection around them
  * (ring_swa/sliding_window/nonvarlen.py:95-150, ring_swa/ops/attn.py:12-60). */
@@ -93,6 +94,13 @@ typedef struct rswa_fwd_params {
   int64_t lse_stride_b, lse_stride_h;
   int32_t q_tile_begin, q_tile_end;
   int32_t* status; /* device word; set non-zero if a device-side wait ran out */
+  /* non-zero: out / lse already hold a partial result over OTHER keys (an earlier call with other
+   * spans); this call continues it -- running maximum and weight start from lse, the accumulator from
+   * out -- and overwrites both with the combined result, as merge_attn_out would have combined two
+   * partial results (ring_swa/ops/attn.py:31-36, ring_swa/ops/merge.py:68-147).  Rows that see no key of
+   * this call's spans keep what they hold. */
+  int32_t carry;
+  int32_t reserved;
 } rswa_fwd_params_t;
 
 int rswa_fwd(const rswa_fwd_params_t* p, void* stream);
@@ -219,6 +227,21 @@ int rswa_halo_accumulate_cast(void* dst, int64_t dst_stride_b, int32_t dst_dtype
  * ring_swa/sliding_window/nonvarlen.py:335-337. */
 int rswa_cast_from_f32(void* dst, int64_t dst_stride_b, const float* src, int64_t src_stride_b,
                        int32_t dtype, int32_t batch, int64_t elems_per_batch, void* stream);
+
+/* Peer-store halo exchange between the GPUs of one node (buffers in memory the receiver owns and the
+ * sender has mapped, e.g. torch symmetric memory; this library maps nothing itself).
+ * rswa_peer_put: copy `rows` rows of `row_bytes` bytes from src (local) to dst (local or a peer's), with
+ * the given pitches, on the copy engines (no kernel, no SM), then, if flag is non-NULL, release `value`
+ * into *flag (local or a peer's) from a one-thread kernel behind the copy on the same stream.
+ * rswa_flag_set: that release alone (an acknowledgement).
+ * rswa_flag_wait: a one-thread kernel that returns once *flag (local memory) has reached `value`
+ * (numbers only grow; wrap-safe) -- what is launched behind it on the stream then finds the data the
+ * number announces -- or, after timeout_ns, sets *status to a non-zero code and returns.
+ * Replaces ring_attn_p2p_communicate (ring_swa/ops/comm.py:8-40: NCCL isend / irecv per hop). */
+int rswa_peer_put(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t row_bytes,
+                  int64_t rows, int32_t* flag, int32_t value, void* stream);
+int rswa_flag_set(int32_t* flag, int32_t value, void* stream);
+int rswa_flag_wait(const int32_t* flag, int32_t value, int32_t* status, int64_t timeout_ns, void* stream);
 
 /* One 128x128x128 tensor-core product through each operand path the attention kernels use
  * (shared-memory K-major / MN-major operands, tensor-memory A operand); for the unit tests.

@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "ring_swa", "librswa.so")
-SOURCES = ["rswa_api.cu", "rswa_fwd.cu", "rswa_bwd.cu", "rswa_dq.cu", "rswa_aux.cu", "rswa_selftest.cu", "rswa_noalloc.cu"]
+SOURCES = ["rswa_api.cu", "rswa_fwd.cu", "rswa_bwd.cu", "rswa_dq.cu", "rswa_aux.cu", "rswa_selftest.cu", "rswa_noalloc.cu", "rswa_peer.cu"]
 HEADERS = ["tc05.cuh", "rswa_common.cuh", "rswa_tiles.cuh", os.path.join("..", "..", "include", "rswa.h")]
 
 

@@ -260,6 +260,7 @@ extern "C" int rswa_fwd(const rswa_fwd_params_t* p, void* stream) {
   kp.l_sh = p->lse_stride_h;
   kp.q_tile_begin = qb;
   kp.n_q_tiles = qe - qb;
+  kp.carry = p->carry != 0;
   kp.status = p->status;
   return launch_fwd(kp, g.dtype, static_cast<cudaStream_t>(stream));
 }

@@ -39,6 +39,7 @@ struct FwdKernelParams {
   float* lse;
   long long l_sb, l_sh;
   int q_tile_begin, n_q_tiles;
+  int carry;  // out / lse hold a partial result over other keys: continue it instead of starting over
   int* status;
 };
 

@@ -34,6 +34,8 @@
 // value dtype before P V.
 #include "rswa_common.cuh"
 #include "rswa_tiles.cuh"
+#include <cuda_fp16.h>
+
 #include "tc05.cuh"
 
 namespace rswa {
@@ -93,7 +95,9 @@ __device__ __forceinline__ FwdItem fwd_item(const FwdKernelParams& p, int n_bloc
   return d;
 }
 
-template <bool kBf16>
+// kCarry: out / lse hold a partial result that the call continues (a variant of its own, so that the
+// plain kernel carries none of that code: its speed is sensitive to its size)
+template <bool kBf16, bool kCarry>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p, int n_blocks, int n_items) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -288,7 +292,7 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p, int n_blocks, int n_i
                 tc_fence_after();
 #pragma unroll
                 for (int k = 4 * half; k < 4 * half + 4; ++k) {
-                  mma_ts(tOw, tSw + k * 8, dVs + k * 128, idesc_pv, (k > 0) ? 1u : ((pv_any >> w) & 1u));
+                  mma_ts(tOw, tSw + k * 8, dVs + k * 128, idesc_pv, (k > 0 || kCarry) ? 1u : ((pv_any >> w) & 1u));
                 }
               }
               if (!ok) break;
@@ -380,6 +384,41 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p, int n_blocks, int n_i
         if (tile_active(geom, w, cur, p.n_sink)) {
           const int kt0 = cur.kt0;
           const int span_end = cur.kt_last + 1;
+          if (kCarry && n_done == 0) {
+            // Continue the partial result that out / lse already hold (over other keys): the running
+            // maximum is its lse, its weight 1, and O starts as its rows (zero where it saw no key).
+            // This warp read O of the previous item out before it got here, and the first product of
+            // this item comes after the P this warp hands over further down.
+            const long long orow = wi.b * p.o_sb + static_cast<long long>((wi.tile0 + w) * kTile + row) * p.o_st + wi.h * p.o_sh;
+            const float lp = valid ? p.lse[wi.b * p.l_sb + wi.h * p.l_sh + (wi.tile0 + w) * kTile + row] : -INFINITY;
+            const bool had = lp > -INFINITY;
+            m_ref = had ? lp * 1.4426950408889634f : -INFINITY;
+            l_sum = had ? 1.f : 0.f;
+            const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.out) + orow);
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+#pragma unroll
+              for (int v4 = 0; v4 < 4; ++v4) {
+                const uint4 x = had ? src[c * 4 + v4] : make_uint4(0, 0, 0, 0);
+                const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  if constexpr (kBf16) {
+                    o[v4 * 8 + 2 * e] = xw[e] << 16;
+                    o[v4 * 8 + 2 * e + 1] = xw[e] & 0xffff0000u;
+                  } else {
+                    const __half2 hh = *reinterpret_cast<const __half2*>(&xw[e]);
+                    const float2 ff = __half22float2(hh);
+                    o[v4 * 8 + 2 * e] = __float_as_uint(ff.x);
+                    o[v4 * 8 + 2 * e + 1] = __float_as_uint(ff.y);
+                  }
+                }
+              }
+              tmem_st32(tO + c * 32, o);
+            }
+            tmem_st_wait();
+          }
           ok = mbar_wait(&ctl->s_ready[w], n_tot & 1, err, kErrWaitSoftmax);
           ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the TMEM accesses
           if (!ok) break;
@@ -460,11 +499,14 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p, int n_blocks, int n_i
             alpha = ex2f(m_ref - mt);  // 0 when m_ref is -inf
             m_ref = mt;
           }
-          if (n_done > 0 && __any_sync(0xffffffffu, grow)) {
-            // O_w must be at rest: wait for the product of the previous tile
-            ok = mbar_wait(&ctl->pv_done[w], (n_tot - 1) & 1, err, kErrWaitSoftmax);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+          if ((n_done > 0 || kCarry) && __any_sync(0xffffffffu, grow)) {
+            // O_w must be at rest: wait for the product of the previous tile (none yet on an item's first
+            // tile, where O_w is the carried-in partial result this warp has just written)
+            if (n_done > 0) {
+              ok = mbar_wait(&ctl->pv_done[w], (n_tot - 1) & 1, err, kErrWaitSoftmax);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+            }
             tc_fence_after();
             l_sum *= alpha;
 #pragma unroll 1
@@ -575,14 +617,15 @@ rswa_fwd_kernel(const __grid_constant__ FwdKernelParams p, int n_blocks, int n_i
           }
           __syncwarp();  // the staging rows are rewritten by the next pass / item
         }
-      } else if (valid) {
-        // no key of the given spans is visible to this query tile: zero rows
+      } else if (valid && !kCarry) {
+        // no key of the given spans is visible to this query tile: zero rows (a carried-in partial
+        // result stays as it is)
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + wi.b * p.o_sb +
                                               static_cast<long long>(tile_row0 + row) * p.o_st + wi.h * p.o_sh);
 #pragma unroll
         for (int v = 0; v < 16; ++v) dst[v] = make_uint4(0, 0, 0, 0);
       }
-      if (valid) {
+      if (valid && (n_done > 0 || !kCarry)) {
         p.lse[wi.b * p.l_sb + wi.h * p.l_sh + tile_row0 + row] =
             has ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
       }
@@ -612,14 +655,16 @@ int launch_fwd(const FwdKernelParams& kp, int dtype, cudaStream_t stream) {
     set_error("rswa_fwd: too many query tiles (%lld)", n_items);
     return RSWA_E_ARG;
   }
-  auto kern = dtype == RSWA_DTYPE_BF16 ? rswa_fwd_kernel<true> : rswa_fwd_kernel<false>;
+  auto kern = dtype == RSWA_DTYPE_BF16 ? (kp.carry ? rswa_fwd_kernel<true, true> : rswa_fwd_kernel<true, false>)
+                                       : (kp.carry ? rswa_fwd_kernel<false, true> : rswa_fwd_kernel<false, false>);
   // (the attribute is a property of the function on a device: set once per kernel variant and device)
-  static bool attr_set[2][64] = {{false}};
+  static bool attr_set[4][64] = {{false}};
+  const int variant = (dtype == RSWA_DTYPE_BF16 ? 1 : 0) + (kp.carry ? 2 : 0);
   int dev_id = 0;
   cudaError_t e = cudaGetDevice(&dev_id);
-  if (e == cudaSuccess && (dev_id < 0 || dev_id >= 64 || !attr_set[dtype == RSWA_DTYPE_BF16][dev_id])) {
+  if (e == cudaSuccess && (dev_id < 0 || dev_id >= 64 || !attr_set[variant][dev_id])) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kFwdSmemBytes);
-    if (e == cudaSuccess && dev_id >= 0 && dev_id < 64) attr_set[dtype == RSWA_DTYPE_BF16][dev_id] = true;
+    if (e == cudaSuccess && dev_id >= 0 && dev_id < 64) attr_set[variant][dev_id] = true;
   }
   if (e != cudaSuccess) {
     set_error("rswa_fwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));

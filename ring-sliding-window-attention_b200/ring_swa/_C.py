@@ -45,6 +45,7 @@ class FwdParams(C.Structure):
         ("lse", C.c_void_p), ("lse_stride_b", C.c_int64), ("lse_stride_h", C.c_int64),
         ("q_tile_begin", C.c_int32), ("q_tile_end", C.c_int32),
         ("status", C.c_void_p),
+        ("carry", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -104,6 +105,10 @@ SYMBOLS = {
                                             C.c_int32, C.c_int32, C.c_int64, C.c_void_p]),
     "rswa_cast_from_f32": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                      C.c_int64, C.c_void_p]),
+    "rswa_peer_put": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int32,
+                                C.c_void_p]),
+    "rswa_flag_set": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p]),
+    "rswa_flag_wait": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p]),
     "rswa_event_create": (C.c_void_p, []),
     "rswa_event_destroy": (None, [C.c_void_p]),
     "rswa_event_record": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -193,16 +193,20 @@ def _fill_geom(g: _C.Geom, q: torch.Tensor, spans: Sequence[KVSpan], window: int
 
 def fwd(q: torch.Tensor, spans: Sequence[KVSpan], window: int, n_sink: int, scale: float, q_pos_start: int = 0,
         cu_seqlens: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-        lse: Optional[torch.Tensor] = None, q_tiles: Optional[Tuple[int, int]] = None
+        lse: Optional[torch.Tensor] = None, q_tiles: Optional[Tuple[int, int]] = None, carry: bool = False
         ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """out [B,S,Hq,D] (input dtype) and lse [B,Hq,S] (fp32) over the given spans."""
+    """out [B,S,Hq,D] (input dtype) and lse [B,Hq,S] (fp32) over the given spans.  With `carry`, out and
+    lse (both required then) hold a partial result over other keys, which this call continues in place."""
     _check4("q", q)
     B, S, Hq, D = q.shape
+    if carry and (out is None or lse is None):
+        raise ValueError("carry needs the out and lse of the partial result to continue")
     if out is None:
         out = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
     if lse is None:
         lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
     p = _C.FwdParams()
+    p.carry = 1 if carry else 0
     _fill_geom(p.g, q, spans, window, n_sink, scale, q_pos_start, cu_seqlens, grads=False)
     p.q = q.data_ptr()
     p.q_stride_b, p.q_stride_t, p.q_stride_h = q.stride(0), q.stride(1), q.stride(2)
@@ -406,6 +410,33 @@ def cast_from_f32(dst: torch.Tensor, src: torch.Tensor) -> None:
     _, ssb, _ = _rows(src)
     _C.check(_C.lib().rswa_cast_from_f32(dst.data_ptr(), dsb, src.data_ptr(), ssb, _dtype_code(dst), B, n,
                                          _stream()), "rswa_cast_from_f32")
+    global launch_count
+    launch_count += 1
+
+
+def peer_put(dst_ptr: int, dst_pitch: int, src: torch.Tensor, flag_ptr: int, value: int) -> None:
+    """Copy-engine transfer of src ([rows, ...] with contiguous rows, local) to dst_ptr (local or a mapped
+    peer address, rows dst_pitch bytes apart) on the current stream, then release `value` into the flag
+    word at flag_ptr (0: no flag)."""
+    rows, sb, n = _rows(src)
+    es = src.element_size()
+    _C.check(_C.lib().rswa_peer_put(dst_ptr, int(dst_pitch), src.data_ptr(), sb * es if rows > 1 else n * es, n * es, rows,
+                                    flag_ptr if flag_ptr else None, int(value), _stream()), "rswa_peer_put")
+    global launch_count
+    launch_count += 1 if flag_ptr else 0
+
+
+def flag_set(flag_ptr: int, value: int) -> None:
+    _C.check(_C.lib().rswa_flag_set(flag_ptr, int(value), _stream()), "rswa_flag_set")
+    global launch_count
+    launch_count += 1
+
+
+def flag_wait(flag_ptr: int, value: int, device: torch.device, timeout_s: float = 5.0) -> None:
+    """Everything launched on the current stream after this starts once the flag has reached `value`; if it
+    has not within timeout_s, the device status word is raised instead (see check_device_status)."""
+    _C.check(_C.lib().rswa_flag_wait(flag_ptr, int(value), status_word(device).data_ptr(), int(timeout_s * 1e9),
+                                     _stream()), "rswa_flag_wait")
     global launch_count
     launch_count += 1
 

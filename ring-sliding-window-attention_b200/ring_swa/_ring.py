@@ -5,7 +5,7 @@ Forward, on rank r of cp (sequence split contiguously, chunk i on group rank i):
   2. while they fly, run the query tiles that only see local keys;
   3. when the halo has landed, run the remaining tiles over sink | halo | local in ONE pass
      (no per-hop partial results), or, when the window spans the whole chunk (W >= S), run the
-     halo as a second partial and fold it in with the log-sum-exp merge kernel.
+     local keys first and let the halo pass continue that partial result inside the kernel.
 Backward mirrors it: K/V gradients of halo (and remote sink) tokens are computed first and sent
 back to their owners while the local part runs; the owner adds them in fp32 and rounds once.
 
@@ -132,8 +132,9 @@ class RingAttn(torch.autograd.Function):
         else:
             K.fwd(q4, near, out=out, lse=lse, **args)
             _wait(halo_works)
-            o2, lse2 = K.fwd(q4, halo_spans[::-1], **args)
-            K.merge(out, lse, o2, lse2)
+            # the halo pass continues the local partial result inside the kernel (no second buffer, no
+            # separate merge pass)
+            K.fwd(q4, halo_spans[::-1], out=out, lse=lse, carry=True, **args)
         _wait(halo_works)
 
         ctx.save_for_backward(q4, k4, v4, out, lse, cu_seqlens,

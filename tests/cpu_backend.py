@@ -22,7 +22,7 @@ def _cu_list(cu):
     return None if cu is None else [int(x) for x in cu.tolist()]
 
 
-def fwd(q, spans, window, n_sink, scale, q_pos_start=0, cu_seqlens=None, out=None, lse=None, q_tiles=None):
+def fwd(q, spans, window, n_sink, scale, q_pos_start=0, cu_seqlens=None, out=None, lse=None, q_tiles=None, carry=False):
     B, S, Hq, D = q.shape
     if out is None:
         out = torch.zeros_like(q)
@@ -32,12 +32,15 @@ def fwd(q, spans, window, n_sink, scale, q_pos_start=0, cu_seqlens=None, out=Non
     if b <= a:
         return out, lse
     if not spans:
-        out[:, a:b] = 0
-        lse[:, :, a:b] = float("-inf")
+        if not carry:
+            out[:, a:b] = 0
+            lse[:, :, a:b] = float("-inf")
         return out, lse
     k, v, pos = _cat(spans)
     o, l = dense_attn(q[:, a:b], k, v, window, scale, n_sink, _cu_list(cu_seqlens), q_pos0=q_pos_start + a,
                       k_pos=pos)
+    if carry:
+        o, l = merge_partials(out[:, a:b].float(), lse[:, :, a:b], o.float(), l)
     out[:, a:b] = o.to(out.dtype)
     lse[:, :, a:b] = l
     return out, lse

@@ -198,6 +198,21 @@ def test_two_phase_forward_and_split_backward():
     K.merge(o1, l1, o2, l2)
     assert_close("out(merge)", o1, ro)
     assert_lse_close(l1, rl)
+    # (b') the halo pass continues the local partial result inside the kernel, in place
+    o3, l3 = K.fwd(q, [local], W, 0, scale, 300)
+    K.fwd(q, [halo], W, 0, scale, 300, out=o3, lse=l3, carry=True)
+    assert_close("out(carried)", o3, ro)
+    assert_lse_close(l3, rl)
+    # ... and the other way round: the halo first (rows beyond its reach start empty, lse = -inf), then
+    # the local keys carried on top; rows that see nothing of the second call keep what they hold
+    o4, l4 = K.fwd(q, [halo], W, 0, scale, 300)
+    K.fwd(q, [local], W, 0, scale, 300, out=o4, lse=l4, carry=True)
+    assert_close("out(carried, halo first)", o4, ro)
+    assert_lse_close(l4, rl)
+    o5, l5 = o4.clone(), l4.clone()
+    far = K.KVSpan(kh, vh, 100000)          # keys no query of this call can see
+    K.fwd(q, [far], W, 0, scale, 300, out=o5, lse=l5, carry=True)
+    assert torch.equal(o5, o4) and torch.equal(l5, l4)
     # (c) backward in two calls sharing the workspace
     dq = torch.empty_like(q)
     halo.dk, halo.dv = torch.empty_like(kh), torch.empty_like(vh)
