@@ -24,6 +24,7 @@ import torch.distributed as dist
 
 from . import _C
 from . import _kernels as K
+from . import _peer
 from ._plan import RingPlan, make_plan
 
 # dtype the halo / sink gradients travel in (None: the input dtype, like the per-hop partials of
@@ -102,16 +103,42 @@ class RingAttn(torch.autograd.Function):
             sbuf = torch.empty((2, B, sr.n) + tuple(k4.shape[2:]), dtype=k4.dtype, device=k4.device)
             sink_ops.append(dist.P2POp(dist.irecv, sbuf, ring.global_rank(sr.owner), ring.group))
             sink_spans.append(K.KVSpan(sbuf[0], sbuf[1], sr.pos_start))
-        packed = {}
-        for s in plan.halo_send:
-            if s.length not in packed:
-                packed[s.length] = _pack_tail(k4, v4, s.length)
-            halo_ops.append(dist.P2POp(dist.isend, packed[s.length], ring.global_rank(s.dst), ring.group))
+        # Halo K/V: peer stores into the receivers' buffers where the ranks are GPUs of one node (no
+        # communication kernel runs next to the attention kernels), torch.distributed messages otherwise.
+        link = None
+        if ring.cp > 1 and q4.is_cuda and _peer.wanted():
+            link = _peer.link_for(ring.group, q4.device, ring.cp, S, window, B, k4.shape[2], D)
         halo_spans = []
-        for r in plan.halo_recv:
-            hbuf = torch.empty((2, B, r.length) + tuple(k4.shape[2:]), dtype=k4.dtype, device=k4.device)
-            halo_ops.append(dist.P2POp(dist.irecv, hbuf, ring.global_rank(r.src), ring.group))
-            halo_spans.append(K.KVSpan(hbuf[0], hbuf[1], r.pos_start))
+        halo_shape = lambda r: (2, B, r.length) + tuple(k4.shape[2:])  # noqa: E731
+        if link is not None:
+            ready = torch.cuda.Event()
+            ready.record()
+            for s in plan.halo_send:
+                link.put(0, s.hop, s.dst, [k4[:, S - s.length:], v4[:, S - s.length:]], ready)
+        else:
+            packed = {}
+            for s in plan.halo_send:
+                if s.length not in packed:
+                    packed[s.length] = _pack_tail(k4, v4, s.length)
+                halo_ops.append(dist.P2POp(dist.isend, packed[s.length], ring.global_rank(s.dst), ring.group))
+            for r in plan.halo_recv:
+                hbuf = torch.empty(halo_shape(r), dtype=k4.dtype, device=k4.device)
+                halo_ops.append(dist.P2POp(dist.irecv, hbuf, ring.global_rank(r.src), ring.group))
+                halo_spans.append(K.KVSpan(hbuf[0], hbuf[1], r.pos_start))
+
+        def halos_landed():
+            """Behind this call on the current stream the halo spans hold their data."""
+            _wait(halo_works)
+            if link is not None and not halo_spans:
+                for r in plan.halo_recv:
+                    n = link.arrived(0, r.hop)
+                    # out of the shared slot into a tensor of this call (the backward needs it again, and
+                    # the sender may reuse the slot for its next message once it is told so)
+                    hbuf = torch.empty(halo_shape(r), dtype=k4.dtype, device=k4.device)
+                    hbuf.copy_(link.slot_view(0, r.hop, halo_shape(r), k4.dtype))
+                    link.release(0, r.hop, r.src, n)
+                    halo_spans.append(K.KVSpan(hbuf[0], hbuf[1], r.pos_start))
+
         sink_works = _exchange(sink_ops)
         halo_works = _exchange(halo_ops)
 
@@ -121,17 +148,17 @@ class RingAttn(torch.autograd.Function):
         args = dict(window=window, n_sink=n_sink, scale=softmax_scale, q_pos_start=pos0, cu_seqlens=cu_seqlens)
         _wait(sink_works)
         near = sink_spans + [local]
-        if not halo_spans:
+        if not plan.halo_recv:
             K.fwd(q4, near, out=out, lse=lse, **args)
         elif window < S:
             nb = plan.halo_tile_end
             K.fwd(q4, near, out=out, lse=lse, q_tiles=(nb, plan.n_tiles), **args)
-            _wait(halo_works)
+            halos_landed()
             spans = sink_spans + halo_spans[::-1] + [local]
             K.fwd(q4, spans, out=out, lse=lse, q_tiles=(0, nb), **args)
         else:
             K.fwd(q4, near, out=out, lse=lse, **args)
-            _wait(halo_works)
+            halos_landed()
             # the halo pass continues the local partial result inside the kernel (no second buffer, no
             # separate merge pass)
             K.fwd(q4, halo_spans[::-1], out=out, lse=lse, carry=True, **args)
@@ -140,7 +167,7 @@ class RingAttn(torch.autograd.Function):
         ctx.save_for_backward(q4, k4, v4, out, lse, cu_seqlens,
                               *[t for s in halo_spans for t in (s.k, s.v)],
                               *[t for s in sink_spans for t in (s.k, s.v)])
-        ctx.plan, ctx.ring, ctx.args, ctx.varlen = plan, ring, args, varlen
+        ctx.plan, ctx.ring, ctx.args, ctx.varlen, ctx.link = plan, ring, args, varlen, link
         return out.squeeze(0) if varlen else out
 
     @staticmethod
@@ -178,21 +205,32 @@ class RingAttn(torch.autograd.Function):
 
         dq4 = torch.empty_like(q4)
         ws = K.bwd_workspace(q4)
-        ops, recvs = [], []
+        link = ctx.link
+        ops, recvs = [], []   # recvs: (offset, tokens, gradient tensor, (hop, sender) when it sits in a peer slot)
         if remote:
             K.bwd(q4, remote, out, lse, do4, dq4, workspace=ws, flags=_C.BWD_INIT, **args)
-            for r, g in zip(plan.halo_recv, remote_grads):
-                ops.append(dist.P2POp(dist.isend, g, ring.global_rank(r.src), ring.group))
+            if link is not None:
+                ready = torch.cuda.Event()
+                ready.record()
+                for r, g in zip(plan.halo_recv, remote_grads):
+                    link.put(1, r.hop, r.src, [g], ready)
+            else:
+                for r, g in zip(plan.halo_recv, remote_grads):
+                    ops.append(dist.P2POp(dist.isend, g, ring.global_rank(r.src), ring.group))
             for sr, g in zip(plan.sink_recv, sink_grads):
                 ops.append(dist.P2POp(dist.isend, g, ring.global_rank(sr.owner), ring.group))
         for s in plan.halo_send:
-            g = grad_pair((B, s.length) + tuple(k4.shape[2:]))
-            ops.append(dist.P2POp(dist.irecv, g, ring.global_rank(s.dst), ring.group))
-            recvs.append((S - s.length, s.length, g))
+            if link is not None:
+                g = link.slot_view(1, s.hop, (2, B, s.length) + tuple(k4.shape[2:]), wire)
+                recvs.append((S - s.length, s.length, g, (s.hop, s.dst)))
+            else:
+                g = grad_pair((B, s.length) + tuple(k4.shape[2:]))
+                ops.append(dist.P2POp(dist.irecv, g, ring.global_rank(s.dst), ring.group))
+                recvs.append((S - s.length, s.length, g, None))
         for s in plan.sink_send:
             g = grad_pair((B, s.n) + tuple(k4.shape[2:]))
             ops.append(dist.P2POp(dist.irecv, g, ring.global_rank(s.dst), ring.group))
-            recvs.append((s.offset, s.n, g))
+            recvs.append((s.offset, s.n, g, None))
         works = _exchange(ops)
 
         # dK and dV are one stacked tensor, so that K and V parts go through the helper kernels together
@@ -204,8 +242,8 @@ class RingAttn(torch.autograd.Function):
         # gradients straight into dk/dv, the tail into a small accumulator.
         acc, acc0 = None, 0
         if recvs:
-            acc0 = min(off for off, _n, _g in recvs)
-            if any(off + n != S for off, n, _g in recvs) or acc0 <= 0 or len(remote) + 2 > _C.RSWA_MAX_SPANS:
+            acc0 = min(r[0] for r in recvs)
+            if any(r[0] + r[1] != S for r in recvs) or acc0 <= 0 or len(remote) + 2 > _C.RSWA_MAX_SPANS:
                 acc0 = 0
             acc = torch.empty((2, B, S - acc0) + tuple(k4.shape[2:]), dtype=torch.float32, device=k4.device)
             local = [K.KVSpan(k4[:, acc0:], v4[:, acc0:], plan.q_pos_start + acc0, dk=acc[0], dv=acc[1])]
@@ -226,13 +264,19 @@ class RingAttn(torch.autograd.Function):
             L = S - acc0
             flat = lambda t: t.reshape((2 * B,) + tuple(t.shape[2:]))  # noqa: E731  (views: [2, B, ...] is contiguous over [2, B])
             recvs.sort(key=lambda r: r[1])
+            # gradients that sit in a peer slot: wait for them to land (in the order they were sent)
+            landed = {}
+            for r in sorted((r for r in recvs if r[3] is not None), key=lambda r: r[3][0]):
+                landed[r[3]] = link.arrived(1, r[3][0])
             last = recvs[-1] if recvs[-1][0] == acc0 and recvs[-1][1] == L else None
-            for off, n_tok, g in (recvs[:-1] if last is not None else recvs):
+            for off, n_tok, g, _slot in (recvs[:-1] if last is not None else recvs):
                 K.halo_accumulate(flat(acc)[:, off - acc0:off - acc0 + n_tok], flat(g))
             if last is not None:
                 K.halo_accumulate_cast(flat(dkv)[:, acc0:], flat(acc), flat(last[2]))
             else:
                 K.cast_from_f32(flat(dkv)[:, acc0:], flat(acc))
+            for (hop, sender), n_msg in landed.items():   # the slots have been read: their senders may reuse them
+                link.release(1, hop, sender, n_msg)
         if q4.is_cuda:
             K.mirror_status(q4.device)
         if varlen:

@@ -319,3 +319,29 @@ def test_backward_called_first_from_a_fresh_thread():
     torch.cuda.synchronize()
     for a, b in zip(got, ref):
         assert torch.equal(a, b)      # the backward is deterministic
+
+
+def test_peer_put_and_bounded_flag_wait():
+    """The pieces of the peer-store exchange on one GPU (destination and flag in local memory): a strided
+    source lands densely and the flag carries its number; a wait for a number that nobody writes gives up
+    after its limit and reports through the status word, leaving the context usable."""
+    K = _K()
+    dev = torch.device("cuda")
+    big = torch.arange(4 * 3000, dtype=torch.float32, device=dev).reshape(4, 3000)
+    src = big[:, 1000:2000]                      # rows of 1000 floats, 3000 apart
+    dst = torch.zeros(4, 1000, dtype=torch.float32, device=dev)
+    flags = torch.zeros(8, dtype=torch.int32, device=dev)
+    K.peer_put(dst.data_ptr(), 4000, src, flags.data_ptr(), 7)
+    K.flag_wait(flags.data_ptr(), 7, dev, timeout_s=2.0)
+    after = dst.clone()                          # launched behind the wait: sees the data
+    torch.cuda.synchronize()
+    assert torch.equal(after, src) and int(flags[0]) == 7
+    K.check_device_status()
+    K.flag_wait(flags.data_ptr(), 5, dev, timeout_s=2.0)      # numbers only grow: an older one is reached already
+    K.check_device_status()
+    K.flag_wait(flags[1:].data_ptr(), 1, dev, timeout_s=0.02)   # nobody writes this word
+    with pytest.raises(RuntimeError, match="device-side error code 105"):
+        K.check_device_status()
+    K.flag_set(flags[1:].data_ptr(), 1)
+    K.flag_wait(flags[1:].data_ptr(), 1, dev, timeout_s=2.0)
+    K.check_device_status()

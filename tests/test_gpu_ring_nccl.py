@@ -25,14 +25,18 @@ def _job(fn, T, B, hq, hkv, W, seed, cu=None, n_sink=0):
                 dtype=torch.bfloat16, expect={k_: v_.float().numpy() for k_, v_ in exp.items()})
 
 
-def _worker(rank, ws, port, jobs, outdir):
+def _worker(rank, ws, port, jobs, outdir, halo):
     torch.cuda.set_device(rank)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ["RING_SWA_HALO"] = halo
     run_rank(rank, ws, port, jobs, outdir, device=f"cuda:{rank}")
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_ring_on_gpus_matches_oracle():
+@pytest.mark.parametrize("halo", ["peer", "nccl"])
+def test_ring_on_gpus_matches_oracle(halo):
+    """Both ways the halos travel: peer stores into the receiver's buffer (the default between GPUs) and
+    torch.distributed point-to-point messages."""
     ws = min(4, torch.cuda.device_count())
     ws = 4 if ws >= 4 else 2
     T = 1024 * ws
@@ -44,7 +48,7 @@ def test_ring_on_gpus_matches_oracle():
         _job("ring_streaming_llm_attn_varlen", T, None, 4, 2, 150, 65, cu=[0, 900, T], n_sink=1),
     ]
     with tempfile.TemporaryDirectory() as tmp:
-        mp.spawn(_worker, args=(ws, 29771, jobs, tmp), nprocs=ws, join=True)
+        mp.spawn(_worker, args=(ws, 29771 if halo == "peer" else 29773, jobs, tmp, halo), nprocs=ws, join=True)
         res = [json.load(open(os.path.join(tmp, f"r{r}.json"))) for r in range(ws)]
     for r, per_rank in enumerate(res):
         for job, errs in zip(jobs, per_rank):
