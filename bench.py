@@ -21,6 +21,9 @@ through the public API on the live process group after the timed region and comp
 out, dq, dk, dv with a dense fp32 torch computation of the global problem;
 `cpu_baseline` is the dense torch CPU restatement of the reference's test oracle on a bounded slice.
 
+`reference_gpu`, when baseline/_ref holds the reference package, is the reference's own GPU path
+(flash-attn 2 + Triton merge) timed on the same GPU and workload in a process of its own
+(`--impl reference_gpu` runs just that).
 `--impl reference` times that CPU restatement alone (the reference's own attention arithmetic lives in
 flash-attn CUDA kernels and has no CPU path; its naive torch oracle is what runs on host cores).
 """
@@ -206,6 +209,54 @@ def run_reference(args, wl):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_gpu(args, wl):
+    """The reference's own GPU path (its ring_swa package from baseline/_ref, flash-attn 2 underneath) on
+    one GPU, same workload and timing as the main arm, in a process of its own (the two packages share
+    their name).  Prints one JSON line; `unavailable` if the package or its kernels do not run here."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    line = {"impl": "reference_gpu", "metric": "ring SWA fwd+bwd tokens/s", "unit": "tokens/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "dtype": "bf16", "data": "synthetic"}
+    try:
+        if not os.path.isdir(os.path.join(ref_dir, "ring_swa")):
+            raise RuntimeError("baseline/_ref holds no ring_swa package (install the reference there first)")
+        for p_ in (PKG, ROOT):
+            while p_ in sys.path:
+                sys.path.remove(p_)
+        sys.path.insert(0, ref_dir)
+        import ring_swa as ref                                # noqa: E402  (the reference's package)
+        if not os.path.abspath(ref.__file__).startswith(os.path.abspath(ref_dir)):
+            raise RuntimeError("ring_swa did not resolve to baseline/_ref")
+        if "varlen" in wl["fn"]:
+            raise RuntimeError("only the batch-row workloads are timed on the reference")
+        dev = torch.device("cuda", 0)
+        B, S, Hq, Hkv, W = wl["B"], wl["S"], wl["Hq"], wl["Hkv"], wl["W"]
+        g = torch.Generator(device=dev).manual_seed(wl["seed"] * 1000)
+        q, k, v, do = (torch.randn(B, S, h, D, device=dev, generator=g).bfloat16() for h in (Hq, Hkv, Hkv, Hq))
+        fn = getattr(ref, wl["fn"])
+
+        def one():
+            q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
+            fn(q, k, v, W, cp_group=None).backward(do)
+            q.grad = k.grad = v.grad = None
+
+        for _ in range(max(args.warmup, 3)):
+            one()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        line.update(value=B * S / (ms * 1e-3), ms_per_step=ms,
+                    config={"workload": f"{args.workload}: reference {wl['fn']}(cp_group=None) B={B} S={S} Hq={Hq} Hkv={Hkv} "
+                                        f"D={D} window={W} fwd+bwd on one GPU through flash-attn"})
+    except Exception as e:                                  # noqa: BLE001  (whatever stops it is the answer)
+        line["unavailable"] = f"{type(e).__name__}: {str(e)[:300]}"
+    print(json.dumps(line), flush=True)
+
+
 def workload_config(args, wl, n):
     s_rank = wl["S"] if args.scaling == "weak" else wl["S"] // n
     return {"workload": f"{args.workload}: {wl['fn']} B={wl['B']} S_global={s_rank * n} S_per_gpu={s_rank} "
@@ -323,18 +374,22 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_gpu"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the strong / weak_small series")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's GPU path (baseline/_ref)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     wl = WORKLOADS[args.workload]
 
     if args.impl == "reference":
         run_reference(args, wl)
+        return
+    if args.impl == "reference_gpu":
+        run_reference_gpu(args, wl)
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -597,6 +652,19 @@ def main():
         if not args.no_e2e:
             line["e2e"] = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d * n,
                            "d2h_bytes_per_step": d2h * n, "ms_per_step": e2e_ms}
+        if n == 1 and not args.no_ref_gpu and os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "ring_swa")):
+            # the reference's GPU path on the same GPU right after ours, for the record (not the reference arm)
+            try:
+                r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference_gpu", "--workload",
+                                    args.workload, "--steps", str(min(args.steps, 10)), "--warmup", "3"],
+                                   capture_output=True, text=True, timeout=300)
+                ref_line = json.loads(r.stdout.strip().splitlines()[-1])
+            except Exception as e:                          # noqa: BLE001
+                ref_line = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+            line["reference_gpu"] = {k_: ref_line.get(k_) for k_ in ("value", "unit", "ms_per_step", "unavailable", "config")
+                                     if ref_line.get(k_) is not None}
+            if ref_line.get("ms_per_step"):
+                line["reference_gpu"]["speedup_of_this_build"] = ref_line["ms_per_step"] / ms_step
         if n == 1 and not args.no_cpu_baseline:
             use_host_cores()
             t = [cpu_pass(CPU_SAMPLE, W, n_sink, wl["seed"])]          # first call warms torch up

@@ -42,6 +42,10 @@ constexpr int kDqCompute = 512;
 // every key tile, and a sleeping poll was measured slower.
 constexpr int kMmaPollNs = 0;
 constexpr int kCmpPollNs = 0;
+#ifndef RSWA_DQ_POLY
+#define RSWA_DQ_POLY 1
+#endif
+constexpr bool kDqPoly = RSWA_DQ_POLY != 0;  // a quarter of the exponentials on the FMA pipe
 constexpr int kDqGeomUsers = 4 + kDqCompute / 32;  // producer, three MMA issuers, one lane per compute warp
 
 struct DqCtl {
@@ -352,8 +356,17 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
           uint32_t s0[32];
           tmem_ld32(tSj + part * 32, s0);
           tmem_ld_wait();
+          // one pair in four goes through the FMA pipe instead of the special-function unit
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pr[i] = ex2f(fmaf(__uint_as_float(s0[i]), sl2, -lse2_r));
+          for (int i = 0; i < 32; i += 2) {
+            const float x0 = fmaf(__uint_as_float(s0[i]), sl2, -lse2_r), x1 = fmaf(__uint_as_float(s0[i + 1]), sl2, -lse2_r);
+            if (kDqPoly && ((i >> 1) & 3) == 3) {
+              const float2 e = ex2_poly2(make_float2(x0, x1));
+              pr[i] = e.x, pr[i + 1] = e.y;
+            } else {
+              pr[i] = ex2f(x0), pr[i + 1] = ex2f(x1);
+            }
+          }
         }
         const bool my_mask = !(kt0 >= lo && kt0 + 31 <= hi && kt0 + 31 < span_end);
         if (__any_sync(0xffffffffu, my_mask)) {

@@ -16,6 +16,8 @@ single-GPU StreamingLLM functions (ring_swa/streaming_llm/naive.py:11-210).
 """
 from __future__ import annotations
 
+import os
+import sys
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -26,6 +28,38 @@ from . import _C
 from . import _kernels as K
 from . import _peer
 from ._plan import RingPlan, make_plan
+
+# Optional tracing: RING_SWA_NVTX=1 wraps the phases of a call in NVTX ranges (visible in a profiler's
+# timeline), RING_SWA_DEBUG=1 logs each call's exchange plan on the host.  Both are off by default and
+# cost one attribute test per phase then.
+_NVTX = os.environ.get("RING_SWA_NVTX", "0") not in ("", "0")
+_DEBUG = os.environ.get("RING_SWA_DEBUG", "0") not in ("", "0")
+
+
+class _phase:
+    """with _phase("name"): an NVTX range when tracing is on, nothing otherwise."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if _NVTX:
+            torch.cuda.nvtx.range_push("ring_swa." + self.name)
+
+    def __exit__(self, *exc):
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
+def _log_plan(what: str, plan, link) -> None:
+    if _DEBUG:
+        print(f"[ring_swa] {what}: rank {plan.rank}/{plan.cp} S={plan.seq_per_rank} W={plan.window} n_sink={plan.n_sink} "
+              f"halo_recv={[(h.src, h.length) for h in plan.halo_recv]} halo_send={[(h.dst, h.length) for h in plan.halo_send]} "
+              f"sink_recv={[(x.owner, x.n) for x in plan.sink_recv]} sink_send={[(x.dst, x.n) for x in plan.sink_send]} "
+              f"halo_tiles=[0,{plan.halo_tile_end}) of {plan.n_tiles} halos_by={'peer stores' if link is not None else 'messages'}",
+              file=sys.stderr, flush=True)
+
 
 # dtype the halo / sink gradients travel in (None: the input dtype, like the per-hop partials of
 # ring_swa/sliding_window/nonvarlen.py:194-195; torch.float32 to send them unrounded)
@@ -147,21 +181,29 @@ class RingAttn(torch.autograd.Function):
         lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q4.device)
         args = dict(window=window, n_sink=n_sink, scale=softmax_scale, q_pos_start=pos0, cu_seqlens=cu_seqlens)
         _wait(sink_works)
+        _log_plan("forward", plan, link)
         near = sink_spans + [local]
         if not plan.halo_recv:
-            K.fwd(q4, near, out=out, lse=lse, **args)
+            with _phase("fwd.local"):
+                K.fwd(q4, near, out=out, lse=lse, **args)
         elif window < S:
             nb = plan.halo_tile_end
-            K.fwd(q4, near, out=out, lse=lse, q_tiles=(nb, plan.n_tiles), **args)
-            halos_landed()
+            with _phase("fwd.tiles_without_halo"):
+                K.fwd(q4, near, out=out, lse=lse, q_tiles=(nb, plan.n_tiles), **args)
+            with _phase("fwd.halo_wait"):
+                halos_landed()
             spans = sink_spans + halo_spans[::-1] + [local]
-            K.fwd(q4, spans, out=out, lse=lse, q_tiles=(0, nb), **args)
+            with _phase("fwd.tiles_with_halo"):
+                K.fwd(q4, spans, out=out, lse=lse, q_tiles=(0, nb), **args)
         else:
-            K.fwd(q4, near, out=out, lse=lse, **args)
-            halos_landed()
+            with _phase("fwd.local"):
+                K.fwd(q4, near, out=out, lse=lse, **args)
+            with _phase("fwd.halo_wait"):
+                halos_landed()
             # the halo pass continues the local partial result inside the kernel (no second buffer, no
             # separate merge pass)
-            K.fwd(q4, halo_spans[::-1], out=out, lse=lse, carry=True, **args)
+            with _phase("fwd.halo_carried"):
+                K.fwd(q4, halo_spans[::-1], out=out, lse=lse, carry=True, **args)
         _wait(halo_works)
 
         ctx.save_for_backward(q4, k4, v4, out, lse, cu_seqlens,
@@ -208,7 +250,8 @@ class RingAttn(torch.autograd.Function):
         link = ctx.link
         ops, recvs = [], []   # recvs: (offset, tokens, gradient tensor, (hop, sender) when it sits in a peer slot)
         if remote:
-            K.bwd(q4, remote, out, lse, do4, dq4, workspace=ws, flags=_C.BWD_INIT, **args)
+            with _phase("bwd.halo_spans"):
+                K.bwd(q4, remote, out, lse, do4, dq4, workspace=ws, flags=_C.BWD_INIT, **args)
             if link is not None:
                 ready = torch.cuda.Event()
                 ready.record()
@@ -255,7 +298,8 @@ class RingAttn(torch.autograd.Function):
         # gradient buffers, their gradients are already on the wire)
         seen = [K.KVSpan(s.k, s.v, s.pos_start) for s in remote]
         flags = _C.BWD_FINISH | (0 if remote else _C.BWD_INIT)
-        K.bwd(q4, seen + local, out, lse, do4, dq4, workspace=ws, flags=flags, **args)
+        with _phase("bwd.local_and_dq"):
+            K.bwd(q4, seen + local, out, lse, do4, dq4, workspace=ws, flags=flags, **args)
         _wait(works)
         if acc is not None:
             # [2, B] is one batch axis for the helper kernels (K and V parts in one launch).  The message
@@ -297,6 +341,18 @@ def ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_glob
 
 def attention(q, k, v, window_size: int, n_sink: int, softmax_scale: Optional[float],
               cu_seqlens: Optional[torch.Tensor], cu_host: Optional[Sequence[int]], ring: RingCtx):
+    head_dim = q.shape[-1]
     if softmax_scale is None:
-        softmax_scale = q.shape[-1] ** (-0.5)
+        softmax_scale = head_dim ** (-0.5)
+    if q.is_cuda and head_dim < K.HEAD_DIM:
+        # The kernels are built for a head dimension of 128.  Smaller ones (the reference's own local
+        # tests use 64) run on them zero-padded: the padding adds nothing to any score, the padded
+        # output and gradient columns are zero and are cut off again -- at the price of the arithmetic
+        # and traffic of a 128-wide head.  The scale keeps referring to the caller's head dimension.
+        if head_dim % 8:
+            raise ValueError(f"head_dim must be a multiple of 8 and at most {K.HEAD_DIM}, got {head_dim}")
+        pad = (0, K.HEAD_DIM - head_dim)
+        q, k, v = (torch.nn.functional.pad(x, pad) for x in (q, k, v))
+        out = RingAttn.apply(q, k, v, int(window_size), int(n_sink), float(softmax_scale), cu_seqlens, cu_host, ring)
+        return out[..., :head_dim]
     return RingAttn.apply(q, k, v, int(window_size), int(n_sink), float(softmax_scale), cu_seqlens, cu_host, ring)

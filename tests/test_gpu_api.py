@@ -87,6 +87,23 @@ def test_device_side_timeout_reaches_the_host_and_clears():
         assert_close(n, a, b)
 
 
+@pytest.mark.parametrize("head_dim", [64, 96])
+def test_smaller_head_dims_run_zero_padded(head_dim):
+    """Head dimensions below 128 (the reference's own local tests use 1 x 1024 x 8/2 heads x 64, window 128:
+    test/test_local_slm.py:76-90) run on the 128-wide kernels zero-padded; result and gradients have the
+    caller's shape and match the oracle at the caller's scale."""
+    import ring_swa
+    q, k, v, do = (randn_bf16(1, 1024, h, head_dim, seed=s) for h, s in ((8, 71), (2, 72), (2, 73), (8, 74)))
+    for fn, ns in ((ring_swa.ring_sliding_window_attn, 0), (ring_swa.ring_streaming_llm_attn, 1)):
+        ro, _, rdq, rdk, rdv = dense_attn_fwd_bwd(q, k, v, do, 128, None, ns)
+        out, dq, dk, dv = _run(fn, q, k, v, do, window_size=128)
+        assert out.shape == q.shape and dk.shape == k.shape
+        for n, a, b in (("out", out, ro), ("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+            assert_close(n, a, b)
+    with pytest.raises(ValueError, match="head_dim"):
+        ring_swa.ring_sliding_window_attn(q[..., :60].cuda(), k[..., :60].cuda(), v[..., :60].cuda(), 128)
+
+
 def test_reference_error_behaviour():
     import ring_swa
     dev = "cuda"
