@@ -553,7 +553,26 @@ def main():
             one()
         a1.record()
         torch.cuda.synchronize()
-        return a0.elapsed_time(a1) / args.steps
+        t_ms = a0.elapsed_time(a1) / args.steps
+        if ranks > 1:      # where the compute stream's time goes, phase by phase (5 more steps, untimed)
+            phase_tables.append(measure_phases(one))
+        return t_ms
+
+    from ring_swa import _ring as ring_impl
+    phase_tables = []
+
+    def measure_phases(one_step, k_steps=5):
+        """[ms per step of each phase of ring_swa._ring.PHASES] on this rank's compute stream."""
+        sync_all()
+        ring_impl.phase_timing(True)
+        for _ in range(k_steps):
+            one_step()
+        t = ring_impl.phase_times()
+        ring_impl.phase_timing(False)
+        return [t[name] / k_steps for name in ring_impl.PHASES]
+
+    if n > 1 and not args.no_extra:
+        phase_tables.append(measure_phases(lambda: step(q, k, v, do)))
 
     extra_ms = [0.0, 0.0, 0.0]      # strong at n ranks, rank 0 alone on the whole sequence, weak_small
     do_extra = not varlen and not args.no_extra and args.scaling == "weak"
@@ -581,6 +600,11 @@ def main():
     if n > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
     ms, fwd_ms, bwd_ms, e2e_ms, dq_ms, strong_ms, alone_ms, small_ms = stats.tolist()
+    phases = None
+    if phase_tables:       # rows: the main (weak) run, then strong and weak_small where they ran; max over ranks
+        pt = torch.tensor(phase_tables, device=dev, dtype=torch.float64)
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        phases = [{name: round(v_, 4) for name, v_ in zip(ring_impl.PHASES, row) if v_ > 0} for row in pt.tolist()]
 
     if rank == 0:
         tokens = B * S_g
@@ -649,6 +673,13 @@ def main():
                 line["strong"] = scaling_obj(wl["S"], ms_step, 1)
                 line["strong"]["efficiency_vs_n1"] = 1.0
             line["weak_small"] = scaling_obj(S_small * n, small_ms, n)
+        if phases:
+            # ms per step of each host-visible phase on the compute stream, max over ranks (CUDA events):
+            # the *_wait entries are the time the compute stream stood still waiting for halo data
+            line["phases_ms"] = phases[0]
+            if do_extra and len(phases) >= 3:
+                line["strong"]["phases_ms"] = phases[1]
+                line["weak_small"]["phases_ms"] = phases[2]
         if not args.no_e2e:
             line["e2e"] = {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d * n,
                            "d2h_bytes_per_step": d2h * n, "ms_per_step": e2e_ms}

@@ -36,8 +36,32 @@ _NVTX = os.environ.get("RING_SWA_NVTX", "0") not in ("", "0")
 _DEBUG = os.environ.get("RING_SWA_DEBUG", "0") not in ("", "0")
 
 
+PHASES = ("fwd.local", "fwd.tiles_without_halo", "fwd.halo_wait", "fwd.tiles_with_halo", "fwd.halo_carried",
+          "bwd.halo_spans", "bwd.local_and_dq", "bwd.grad_wait", "bwd.accumulate")
+_phase_events = None   # list of (name, start event, stop event) while phase timing is on
+
+
+def phase_timing(on: bool) -> None:
+    """Starts (and clears) or stops the recording of one CUDA event pair around every phase on the
+    compute stream.  Off by default; a measurement aid, the product path records nothing."""
+    global _phase_events
+    _phase_events = [] if on else None
+
+
+def phase_times() -> dict:
+    """{phase: total milliseconds on the compute stream} over the calls recorded since phase_timing(True)
+    (synchronises).  `halo_wait` / `grad_wait` are the time the compute stream stood still for data."""
+    out = {name: 0.0 for name in PHASES}
+    if _phase_events:
+        torch.cuda.synchronize()
+        for name, e0, e1 in _phase_events:
+            out[name] += e0.elapsed_time(e1)
+    return out
+
+
 class _phase:
-    """with _phase("name"): an NVTX range when tracing is on, nothing otherwise."""
+    """with _phase("name"): an NVTX range when tracing is on, an event pair when phase timing is on,
+    nothing otherwise."""
 
     def __init__(self, name: str):
         self.name = name
@@ -45,10 +69,17 @@ class _phase:
     def __enter__(self):
         if _NVTX:
             torch.cuda.nvtx.range_push("ring_swa." + self.name)
+        if _phase_events is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record()
 
     def __exit__(self, *exc):
         if _NVTX:
             torch.cuda.nvtx.range_pop()
+        if _phase_events is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record()
+            _phase_events.append((self.name, self.e0, e1))
         return False
 
 
@@ -300,7 +331,8 @@ class RingAttn(torch.autograd.Function):
         flags = _C.BWD_FINISH | (0 if remote else _C.BWD_INIT)
         with _phase("bwd.local_and_dq"):
             K.bwd(q4, seen + local, out, lse, do4, dq4, workspace=ws, flags=flags, **args)
-        _wait(works)
+        with _phase("bwd.grad_wait"):
+            _wait(works)
         if acc is not None:
             # [2, B] is one batch axis for the helper kernels (K and V parts in one launch).  The message
             # that covers the whole accumulator (the nearest later rank's) goes last: its addition and the
@@ -310,15 +342,17 @@ class RingAttn(torch.autograd.Function):
             recvs.sort(key=lambda r: r[1])
             # gradients that sit in a peer slot: wait for them to land (in the order they were sent)
             landed = {}
-            for r in sorted((r for r in recvs if r[3] is not None), key=lambda r: r[3][0]):
-                landed[r[3]] = link.arrived(1, r[3][0])
+            with _phase("bwd.grad_wait"):
+                for r in sorted((r for r in recvs if r[3] is not None), key=lambda r: r[3][0]):
+                    landed[r[3]] = link.arrived(1, r[3][0])
             last = recvs[-1] if recvs[-1][0] == acc0 and recvs[-1][1] == L else None
-            for off, n_tok, g, _slot in (recvs[:-1] if last is not None else recvs):
-                K.halo_accumulate(flat(acc)[:, off - acc0:off - acc0 + n_tok], flat(g))
-            if last is not None:
-                K.halo_accumulate_cast(flat(dkv)[:, acc0:], flat(acc), flat(last[2]))
-            else:
-                K.cast_from_f32(flat(dkv)[:, acc0:], flat(acc))
+            with _phase("bwd.accumulate"):
+                for off, n_tok, g, _slot in (recvs[:-1] if last is not None else recvs):
+                    K.halo_accumulate(flat(acc)[:, off - acc0:off - acc0 + n_tok], flat(g))
+                if last is not None:
+                    K.halo_accumulate_cast(flat(dkv)[:, acc0:], flat(acc), flat(last[2]))
+                else:
+                    K.cast_from_f32(flat(dkv)[:, acc0:], flat(acc))
             for (hop, sender), n_msg in landed.items():   # the slots have been read: their senders may reuse them
                 link.release(1, hop, sender, n_msg)
         if q4.is_cuda:
