@@ -31,6 +31,12 @@
 namespace rswa {
 using namespace tc05;
 
+RSWA_TRACE_DECL(dq)
+#ifndef RSWA_TRACE_G0
+#define RSWA_TRACE_G0 200
+#endif
+#define DQ_TRC(cond, g, s) RSWA_TRC(dq, (cond) && (g) >= RSWA_TRACE_G0 && (g) < RSWA_TRACE_G0 + 32, ((g) - RSWA_TRACE_G0) * 32 + (s))
+
 namespace {
 
 constexpr int kDqThreads = 640;
@@ -77,9 +83,16 @@ __device__ __forceinline__ DqItem dq_item(const BwdKernelParams& p, int n_q_tile
   return d;
 }
 
-template <bool kBf16>
+// kPlain: one KV span, no packed sequences, no sink tokens (the plain sliding window of one GPU).  The
+// SM's instruction cache holds 32 KB and this kernel's five roles together execute more than that per
+// work item, so what such a call cannot need is compiled out of its variant.
+template <bool kBf16, bool kPlain>
 __global__ void __launch_bounds__(kDqThreads, 1)
 rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_items) {
+  const int* const cu_seq = kPlain ? nullptr : p.cu;
+  const int n_seqs = kPlain ? 0 : p.n_seqs;
+  const int n_spans = kPlain ? 1 : p.n_spans;
+  const int n_sink = kPlain ? 0 : p.n_sink;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sDO = smem + kTileBytes;
@@ -138,64 +151,66 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
     setmaxnreg_dec<56>();
     if (warp == 0 && lane == 0) {
       // ------------------------------------------------------------------ key-tile lists + TMA producer
-      bool ok = true;
-      int n = 0, kc = 0, ic = 0;  // items seen, K/V tiles loaded so far, items with work so far
-      for (;; ++n) {
-        const int slot = n & 1;
-        // The list of item n goes into slot n & 1 once every role is done with item n - 2.  This
-        // thread has spare time exactly here: its last loads of the previous item are issued and
-        // the ring stages for this one are still in use.
-        if (n >= 2) ok = mbar_wait<200>(&ctl->geom_free[slot], ((n >> 1) - 1) & 1, err, kErrWaitProducer);
-        if (!ok) break;
-        const int it = n_work > 0 ? atomicAdd(p.dq_counter, 1) : n_work;
-        if (it >= n_work) {  // tell every role that the work has run out
-          ctl->item[slot] = -1;
+      // One loop turn per key tile and ONE copy of each load's code (this thread runs through its code
+      // at the pace of instruction fetch, and the kernel has to fit the instruction cache).
+      int n = -1, kc = 0, ic = 0;  // item of this CTA, K/V tiles loaded so far, items with work so far
+      int j = 0, n_tiles = 0, slot = 0;
+      DqItem w = {};
+      QBlockGeom* geom = nullptr;
+      TileCursor c = {};
+      for (;;) {
+        if (j >= n_tiles) {  // next item
+          if (n >= 0) mbar_arrive(&ctl->geom_free[slot]);  // this role is done with the list of the item before
+          ++n;
+          slot = n & 1;
+          // The list of item n goes into slot n & 1 once every role is done with item n - 2.  This
+          // thread has spare time exactly here: its last loads of the previous item are issued and
+          // the ring stages for this one are still in use.
+          if (n >= 2 && !mbar_wait<200>(&ctl->geom_free[slot], ((n >> 1) - 1) & 1, err, kErrWaitProducer)) break;
+          const int it = n_work > 0 ? atomicAdd(p.dq_counter, 1) : n_work;
+          j = 0;
+          n_tiles = 0;
+          if (it >= n_work) {  // tell every role that the work has run out
+            ctl->item[slot] = -1;
+            mbar_arrive(&ctl->geom_full[slot]);
+            break;
+          }
+          ctl->item[slot] = it;
+          geom = &ctl->geom[slot];
+          w = dq_item(p, n_q_tiles, it);
+          // a block of one query tile: the second tile of the geometry stays empty
+          qblock_geometry<kTile>(geom, cu_seq, n_seqs, n_spans, p.span_pos, p.span_len, p.q_pos_start, p.q_len,
+                                 p.window, n_sink, w.qt, w.qt + 1);
           mbar_arrive(&ctl->geom_full[slot]);
-          break;
-        }
-        ctl->item[slot] = it;
-        QBlockGeom* geom = &ctl->geom[slot];
-        const DqItem w = dq_item(p, n_q_tiles, it);
-        // a block of one query tile: the second tile of the geometry stays empty
-        qblock_geometry<kTile>(geom, p.cu, p.n_seqs, p.n_spans, p.span_pos, p.span_len, p.q_pos_start, p.q_len,
-                               p.window, p.n_sink, w.qt, w.qt + 1);
-        mbar_arrive(&ctl->geom_full[slot]);
-        const int n_tiles = geom->n_tiles;
-        if (n_tiles > 0) {
+          n_tiles = geom->n_tiles;
+          if (n_tiles == 0) continue;
+          cursor_begin<kTile>(geom, p.span_pos, p.span_len, c);
           // Q may be replaced once the last S product of the previous item has read it
-          if (ic > 0) ok = mbar_wait<200>(&ctl->q_free, (ic - 1) & 1, err, kErrWaitProducer);
-          if (!ok) break;
+          if (ic > 0 && !mbar_wait<200>(&ctl->q_free, (ic - 1) & 1, err, kErrWaitProducer)) break;
           mbar_expect_tx(&ctl->q_full, kTileBytes);
           tma_load_4d(sQ, &p.q_map, &ctl->q_full, 0, w.h, w.row0, w.b);
           tma_load_4d(sQ + kBoxBytes, &p.q_map, &ctl->q_full, 64, w.h, w.row0, w.b);
-          TileCursor c;
-          cursor_begin<kTile>(geom, p.span_pos, p.span_len, c);
-          for (int j = 0; j < n_tiles && ok; ++j, ++kc) {
-            const int sk = kc % kDqKStages, sv = kc & 1;
-            if (kc >= kDqKStages)
-              ok = mbar_wait<200>(&ctl->k_free[sk], ((kc / kDqKStages) - 1) & 1, err, kErrWaitProducer);
-            if (!ok) break;
-            mbar_expect_tx(&ctl->k_full[sk], kTileBytes);
-            tma_load_4d(sK + sk * kTileBytes, &p.k_map[c.span], &ctl->k_full[sk], 0, w.hk, c.tok, w.b);
-            tma_load_4d(sK + sk * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[sk], 64, w.hk, c.tok, w.b);
-            if (j == 0) {
-              // dO likewise, after the last dP product of the previous item
-              if (ic > 0) ok = mbar_wait<200>(&ctl->do_free, (ic - 1) & 1, err, kErrWaitProducer);
-              if (!ok) break;
-              mbar_expect_tx(&ctl->do_full, kTileBytes);
-              tma_load_4d(sDO, &p.do_map, &ctl->do_full, 0, w.h, w.row0, w.b);
-              tma_load_4d(sDO + kBoxBytes, &p.do_map, &ctl->do_full, 64, w.h, w.row0, w.b);
-            }
-            if (kc >= 2) ok = mbar_wait<200>(&ctl->v_free[sv], ((kc >> 1) - 1) & 1, err, kErrWaitProducer);
-            if (!ok) break;
-            mbar_expect_tx(&ctl->v_full[sv], kTileBytes);
-            tma_load_4d(sV + sv * kTileBytes, &p.v_map[c.span], &ctl->v_full[sv], 0, w.hk, c.tok, w.b);
-            tma_load_4d(sV + sv * kTileBytes + kBoxBytes, &p.v_map[c.span], &ctl->v_full[sv], 64, w.hk, c.tok, w.b);
-            cursor_next<kTile>(geom, p.span_pos, p.span_len, c, j + 1 < n_tiles);
-          }
-          ++ic;
         }
-        if (ok) mbar_arrive(&ctl->geom_free[slot]);
+        const int sk = kc % kDqKStages, sv = kc & 1;
+        if (kc >= kDqKStages && !mbar_wait<200>(&ctl->k_free[sk], ((kc / kDqKStages) - 1) & 1, err, kErrWaitProducer)) break;
+        mbar_expect_tx(&ctl->k_full[sk], kTileBytes);
+        tma_load_4d(sK + sk * kTileBytes, &p.k_map[c.span], &ctl->k_full[sk], 0, w.hk, c.tok, w.b);
+        tma_load_4d(sK + sk * kTileBytes + kBoxBytes, &p.k_map[c.span], &ctl->k_full[sk], 64, w.hk, c.tok, w.b);
+        if (j == 0) {
+          // dO likewise, after the last dP product of the previous item
+          if (ic > 0 && !mbar_wait<200>(&ctl->do_free, (ic - 1) & 1, err, kErrWaitProducer)) break;
+          ++ic;
+          mbar_expect_tx(&ctl->do_full, kTileBytes);
+          tma_load_4d(sDO, &p.do_map, &ctl->do_full, 0, w.h, w.row0, w.b);
+          tma_load_4d(sDO + kBoxBytes, &p.do_map, &ctl->do_full, 64, w.h, w.row0, w.b);
+        }
+        if (kc >= 2 && !mbar_wait<200>(&ctl->v_free[sv], ((kc >> 1) - 1) & 1, err, kErrWaitProducer)) break;
+        mbar_expect_tx(&ctl->v_full[sv], kTileBytes);
+        tma_load_4d(sV + sv * kTileBytes, &p.v_map[c.span], &ctl->v_full[sv], 0, w.hk, c.tok, w.b);
+        tma_load_4d(sV + sv * kTileBytes + kBoxBytes, &p.v_map[c.span], &ctl->v_full[sv], 64, w.hk, c.tok, w.b);
+        ++j;
+        ++kc;
+        cursor_next<kTile>(geom, p.span_pos, p.span_len, c, j < n_tiles);
       }
     } else if (warp == 1 && elect_one()) {
       // ------------------------------------------------------------------ MMA issuer 1: S = Q K^T
@@ -203,6 +218,9 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       constexpr uint32_t kTile16 = kTileBytes >> 4;
       const uint64_t dQd = smem_desc_sw128(smem_u32(sQ), 16, 1024);
       const uint64_t dKk = smem_desc_sw128(smem_u32(sK), 16, 1024);  // K as K-major B operand
+      uint64_t dqa[8];  // the A operands never change: Q has one buffer
+#pragma unroll
+      for (int k = 0; k < 8; ++k) dqa[k] = dQd + ((((k >> 2) * kBoxBytes + (k & 3) * 32)) >> 4);
       bool ok = true;
       int n = 0, kc = 0, ic = 0;  // kc: key tiles of earlier items = running index of this item's tile 0
       for (;; ++n) {
@@ -215,17 +233,25 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
             const int sk = g % kDqKStages;
+            // every operand of the eight instructions is in a register BEFORE the waits: what this
+            // thread executes between the last barrier and the last instruction is on the chain that
+            // bounds the kernel, and it gets an instruction through only every few cycles
+            uint64_t db[8];
+            const uint32_t td = tmem + 128 * (g & 1);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              db[k] = dKk + sk * kTile16 + ((((k >> 2) * kBoxBytes + (k & 3) * 32)) >> 4);
+              asm volatile("" : "+l"(db[k]));
+            }
             ok = mbar_wait<kMmaPollNs>(&ctl->k_full[sk], (g / kDqKStages) & 1, err, kErrWaitMma);
             // S buffer g & 1 last held dS of tile g - 2: the dQ product that reads it must be complete
             if (ok && g >= 2) ok = mbar_wait<kMmaPollNs>(&ctl->s_free[g & 1], ((g >> 1) - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
+            DQ_TRC(true, g, 0);
             tc_fence_after();
-            const uint64_t dKs = dKk + sk * kTile16;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const uint32_t off = ((k >> 2) * kBoxBytes + (k & 3) * 32) >> 4;
-              mma_ss(tmem + 128 * (g & 1), dQd + off, dKs + off, id_kk, k > 0 ? 1u : 0u);
-            }
+            for (int k = 0; k < 8; ++k) mma_ss(td, dqa[k], db[k], id_kk, k > 0 ? 1u : 0u);
+            DQ_TRC(true, g, 1);
             mma_commit(&ctl->s_ready[g & 1]);
             if (j + 1 == n_tiles) mma_commit(&ctl->q_free);  // that was the item's last read of Q
           }
@@ -249,17 +275,25 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         if (n_tiles > 0) {
           for (int j = 0; j < n_tiles && ok; ++j) {
             const int g = kc + j;
+            // (operands in registers before the waits, as for S)
+            uint64_t db[8];
+            uint32_t ta[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              db[k] = dKm + (g % kDqKStages) * kTile16 + k * 128;
+              ta[k] = tmem + 128 * (g & 1) + (k >> 1) * 32 + (k & 1) * 8;
+              asm volatile("" : "+l"(db[k]), "+r"(ta[k]));
+            }
+            const uint32_t acc0 = j > 0 ? 1u : 0u;
             ok = mbar_wait<kMmaPollNs>(&ctl->ds_ready, g & 1, err, kErrWaitMma);
             // the first product of an item overwrites dQ: the previous item's must have been read out
             if (ok && j == 0 && ic > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dq_drained, (ic - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
+            DQ_TRC(true, g, 2);
             tc_fence_after();
-            const uint64_t dKj = dKm + (g % kDqKStages) * kTile16;
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              mma_ts(tDQ, tmem + 128 * (g & 1) + (k >> 1) * 32 + (k & 1) * 8, dKj + k * 128, id_tn,
-                     (j > 0 || k > 0) ? 1u : 0u);
-            }
+            for (int k = 0; k < 8; ++k) mma_ts(tDQ, ta[k], db[k], id_tn, k > 0 ? 1u : acc0);
+            DQ_TRC(true, g, 3);
             mma_commit(&ctl->k_free[g % kDqKStages]);
             mma_commit(&ctl->s_free[g & 1]);
           }
@@ -291,6 +325,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
             // the compute warps must have read dP of the previous tile out of TMEM
             if (ok && g > 0) ok = mbar_wait<kMmaPollNs>(&ctl->dp_loaded, (g - 1) & 1, err, kErrWaitMma);
             if (!ok) break;
+            DQ_TRC(true, g, 4);
             tc_fence_after();
             const uint64_t dVs = dVk + sv * kTile16;
 #pragma unroll
@@ -299,6 +334,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
               mma_ss(tDP, dDO + off, dVs + off, id_kk, k > 0 ? 1u : 0u);
             }
             mma_commit(&ctl->dp_ready);
+            DQ_TRC(true, g, 5);
             mma_commit(&ctl->v_free[sv]);
           }
           if (ok) mma_commit(&ctl->do_free);
@@ -320,6 +356,47 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
     const float mul = p.scale;
     bool ok = true;
     int n = 0, kc = 0, ic = 0;
+    // row statistics of the item after this one, fetched while this one's last products still run
+    float lse2_nx = 0.f, delta_nx = 0.f;
+    auto row_stats = [&](int it_, float& l2, float& dl) {
+      const DqItem w_ = dq_item(p, n_q_tiles, it_);
+      const long long roff = w_.b * p.d_sb + w_.h * p.d_sh + w_.row0 + row;  // rows are padded to whole tiles
+      l2 = p.lse2[roff];  // +inf past q_len: P vanishes
+      dl = p.delta[roff];
+    };
+    // An item's dQ is read out of tensor memory and stored only after the first exponentials of the
+    // NEXT item: its last product is still running when its last dS has been handed over, and waiting
+    // for it right there left every compute warp idle.
+    uint16_t* pend_row = nullptr;  // where this thread's 32 values of the pending item go (null: row does not exist)
+    bool pend = false;
+    int pend_ic = 0;
+    auto drain = [&]() -> bool {
+      bool k = mbar_wait<kCmpPollNs>(&ctl->done, pend_ic & 1, err, kErrWaitEpilogue);
+      k = __all_sync(0xffffffffu, k);
+      if (!k) return false;
+      tc_fence_after();
+      uint32_t r[32];
+      tmem_ld32(tDQ + lane_off + part * 32, r);
+      tmem_ld_wait();
+      // the accumulator is released as soon as it is in registers
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->dq_drained);
+      if (pend_row != nullptr) {
+        uint4* dst = reinterpret_cast<uint4*>(pend_row);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 o;
+          o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
+          o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
+          o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
+          o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
+          dst[v] = o;
+        }
+      }
+      pend = false;
+      return true;
+    };
     for (;; ++n) {
       const int slot = n & 1;
       ok = mbar_wait<kCmpPollNs>(&ctl->geom_full[slot], (n >> 1) & 1, err, kErrWaitSoftmax);
@@ -328,18 +405,17 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       const int it = ctl->item[slot];
       if (it < 0) break;
       const DqItem w = dq_item(p, n_q_tiles, it);
-      const long long roff = w.b * p.d_sb + w.h * p.d_sh + w.row0 + row;  // rows are padded to whole tiles
-      const float lse2_r = p.lse2[roff];                                  // +inf past q_len: P vanishes
-      const float delta_r = p.delta[roff];
+      if (n == 0) row_stats(it, lse2_nx, delta_nx);
+      const float lse2_r = lse2_nx, delta_r = delta_nx;
       const QBlockGeom* geom = &ctl->geom[slot];
       const int n_tiles = geom->n_tiles;
       const bool valid = row < geom->n_valid[0];
       const int pos = geom->p0[0] + row;
       int s_p = 0, e_p = 0;
-      if (valid) seq_of(p.cu, p.n_seqs, pos, s_p, e_p);
+      if (valid) seq_of(cu_seq, n_seqs, pos, s_p, e_p);
       const int hi = valid ? pos : -1;
       const int lo = valid ? max(s_p, pos - p.window) : 0x7fffffff;
-      const int sink_end = valid ? s_p + p.n_sink : -0x7fffffff;
+      const int sink_end = valid ? s_p + n_sink : -0x7fffffff;
       TileCursor cur;
       cursor_begin<kTile>(geom, p.span_pos, p.span_len, cur);
       for (int j = 0; j < n_tiles && ok; ++j) {
@@ -350,6 +426,8 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         ok = mbar_wait<kCmpPollNs>(&ctl->s_ready[g & 1], (g >> 1) & 1, err, kErrWaitSoftmax);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        DQ_TRC(warp == 4 && lane == 0, g, 8);
+        DQ_TRC(warp == 17 && lane == 0, g, 12);
         tc_fence_after();
         float pr[32];
         {
@@ -370,16 +448,28 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         }
         const bool my_mask = !(kt0 >= lo && kt0 + 31 <= hi && kt0 + 31 < span_end);
         if (__any_sync(0xffffffffu, my_mask)) {
+          // this row sees the positions [lo, top] (its window) and [s_p, s_p + sn) (sink tokens below it)
+          const int top = min(hi, span_end - 1);
+          const uint32_t wn = static_cast<uint32_t>(max(top - lo + 1, 0));
+          const uint32_t sn = kPlain ? 0u : static_cast<uint32_t>(max(min(sink_end, top + 1) - s_p, 0));
+          const int c0 = kt0 - lo, c1 = kt0 - s_p;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int t = kt0 + i;
-            const bool vis = t <= hi && t < span_end && (t >= lo || (t >= s_p && t < sink_end));
+            const bool vis = static_cast<uint32_t>(c0 + i) < wn || (!kPlain && static_cast<uint32_t>(c1 + i) < sn);
             pr[i] = vis ? pr[i] : 0.f;
           }
+        }
+        DQ_TRC(warp == 4 && lane == 0, g, 9);
+        DQ_TRC(warp == 17 && lane == 0, g, 13);
+        if (j == 0 && pend) {
+          ok = drain();
+          if (!ok) break;
         }
         ok = mbar_wait<kCmpPollNs>(&ctl->dp_ready, g & 1, err, kErrWaitSoftmax);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        DQ_TRC(warp == 4 && lane == 0, g, 10);
+        DQ_TRC(warp == 17 && lane == 0, g, 14);
         tc_fence_after();
         uint32_t dpk[16];
         {
@@ -402,45 +492,41 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->ds_ready);
+        DQ_TRC(warp == 4 && lane == 0, g, 11);
+        DQ_TRC(warp == 17 && lane == 0, g, 15);
         cursor_next<kTile>(geom, p.span_pos, p.span_len, cur, j + 1 < n_tiles);
       }
       if (!ok) break;
 
-      // the item's dQ * softmax_scale -> dq; the accumulator is released as soon as it is in registers
-      uint32_t r[32];
-      if (n_tiles > 0) {
-        ok = mbar_wait<kCmpPollNs>(&ctl->done, ic & 1, err, kErrWaitEpilogue);
+      {
+        // the next item's list is ready long before this point (the producer runs an item ahead): its
+        // rows' lse and delta are on their way while the epilogue below runs
+        const int slot_nx = (n + 1) & 1;
+        ok = mbar_wait<kCmpPollNs>(&ctl->geom_full[slot_nx], ((n + 1) >> 1) & 1, err, kErrWaitSoftmax);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        tc_fence_after();
-        tmem_ld32(tDQ + lane_off + part * 32, r);
-        tmem_ld_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->dq_drained);
+        const int it_nx = ctl->item[slot_nx];
+        if (it_nx >= 0) row_stats(it_nx, lse2_nx, delta_nx);
+      }
+      uint16_t* drow = reinterpret_cast<uint16_t*>(p.dq) + w.b * p.dq_sb +
+                       static_cast<long long>(w.row0 + row) * p.dq_st + w.h * p.dq_sh + part * 32;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->geom_free[slot]);  // (the list is not needed any more)
+      if (n_tiles > 0) {
+        // the item's dQ * softmax_scale -> dq: later (see above)
+        pend = true;
+        pend_ic = ic;
+        pend_row = valid ? drow : nullptr;
         kc += n_tiles;
         ++ic;
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) r[i] = 0u;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->geom_free[slot]);
-      if (valid) {
-        uint16_t* drow = reinterpret_cast<uint16_t*>(p.dq) + w.b * p.dq_sb +
-                         static_cast<long long>(w.row0 + row) * p.dq_st + w.h * p.dq_sh + part * 32;
+      } else if (valid) {
+        // no key of the given spans is visible to this query tile
         uint4* dst = reinterpret_cast<uint4*>(drow);
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 o;
-          o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
-          o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
-          o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
-          o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
-          dst[v] = o;
-        }
+        for (int v = 0; v < 4; ++v) dst[v] = make_uint4(0, 0, 0, 0);
       }
     }
+    if (ok && pend) ok = drain();
   }
 
   tc_fence_before();
@@ -462,14 +548,19 @@ int launch_dq(const BwdKernelParams& kp, int dtype, cudaStream_t stream) {
     set_error("rswa_bwd: too many query tiles (%lld)", n_items);
     return RSWA_E_ARG;
   }
-  auto kern = dtype == RSWA_DTYPE_BF16 ? rswa_dq_kernel<true> : rswa_dq_kernel<false>;
+  const bool plain = kp.n_spans == 1 && kp.cu == nullptr && kp.n_sink == 0;
+  const int variant = (dtype == RSWA_DTYPE_BF16 ? 1 : 0) + (plain ? 2 : 0);
+  using Kern = void (*)(const BwdKernelParams, int, int);
+  static const Kern kerns[4] = {rswa_dq_kernel<false, false>, rswa_dq_kernel<true, false>,
+                                rswa_dq_kernel<false, true>, rswa_dq_kernel<true, true>};
+  const Kern kern = kerns[variant];
   // (the attribute is a property of the function on a device: set once per kernel variant and device)
-  static bool attr_set[2][64] = {{false}};
+  static bool attr_set[4][64] = {{false}};
   int dev_id = 0;
   cudaError_t e = cudaGetDevice(&dev_id);
-  if (e == cudaSuccess && (dev_id < 0 || dev_id >= 64 || !attr_set[dtype == RSWA_DTYPE_BF16][dev_id])) {
+  if (e == cudaSuccess && (dev_id < 0 || dev_id >= 64 || !attr_set[variant][dev_id])) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes);
-    if (e == cudaSuccess && dev_id >= 0 && dev_id < 64) attr_set[dtype == RSWA_DTYPE_BF16][dev_id] = true;
+    if (e == cudaSuccess && dev_id >= 0 && dev_id < 64) attr_set[variant][dev_id] = true;
   }
   if (e != cudaSuccess) {
     set_error("rswa_bwd(dq): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
