@@ -31,8 +31,8 @@ __device__ __forceinline__ uint32_t pack2f(float lo, float hi) {
 }
 
 // Half a warp per (b, t, h) row of 128 elements (16 bytes per lane and tensor).  Writes
-// delta = rowsum(dO * O) and lse2 = lse * log2(e) into rows padded to whole 128-query tiles; the
-// padding gets delta = 0 and lse2 = +inf so that P = exp2(s - lse2) vanishes there.
+// -delta = -rowsum(dO * O) and -lse2 = -lse * log2(e) into rows padded to whole 128-query tiles; the
+// padding gets -delta = 0 and -lse2 = -inf so that P = exp2(s - lse2) vanishes there.
 template <bool kBf16>
 __global__ void delta_kernel(const uint16_t* __restrict__ out, long long o_sb, long long o_st, long long o_sh,
                              const uint16_t* __restrict__ dout, long long d_sb, long long d_st, long long d_sh,
@@ -62,8 +62,13 @@ __global__ void delta_kernel(const uint16_t* __restrict__ out, long long o_sb, l
   for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   if (sub == 0) {
     const long long idx = (static_cast<long long>(b) * hq + h) * q_len_pad + t;
-    delta[idx] = s;
-    lse2[idx] = t < q_len ? lse[b * l_sb + h * l_sh + t] * 1.4426950408889634f : INFINITY;
+    // both rows are stored NEGATED: the backward kernels only ever add them (s * scale - lse2, dP - delta),
+    // once per score, and their inner loops are bound by instruction count
+    delta[idx] = -s;
+    // (a row that saw no key at all has lse = -inf: it gets -inf like the padding, so that its P vanishes
+    // whatever its scores are, -inf included, instead of turning into inf - inf)
+    const float l = t < q_len ? lse[b * l_sb + h * l_sh + t] : -INFINITY;
+    lse2[idx] = l > -INFINITY ? l * -1.4426950408889634f : -INFINITY;
   }
 }
 

@@ -63,7 +63,8 @@ struct BwdKernelParams {
   const int* cu;
   int n_seqs;
   // rows prepared by the delta kernel, both [batch, hq, q_len_pad] fp32, 512-byte aligned per
-  // 128-query tile: lse * log2(e) (+inf past q_len) and delta = rowsum(dO * O) (0 past q_len)
+  // 128-query tile and both NEGATED: -lse * log2(e) (-inf past q_len) and -delta = -rowsum(dO * O)
+  // (0 past q_len)
   const float* lse2;
   const float* delta;
   long long d_sb, d_sh;

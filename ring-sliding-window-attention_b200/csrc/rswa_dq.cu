@@ -361,7 +361,7 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
     auto row_stats = [&](int it_, float& l2, float& dl) {
       const DqItem w_ = dq_item(p, n_q_tiles, it_);
       const long long roff = w_.b * p.d_sb + w_.h * p.d_sh + w_.row0 + row;  // rows are padded to whole tiles
-      l2 = p.lse2[roff];  // +inf past q_len: P vanishes
+      l2 = p.lse2[roff];  // (negated) -inf past q_len: P vanishes
       dl = p.delta[roff];
     };
     // An item's dQ is read out of tensor memory and stored only after the first exponentials of the
@@ -383,15 +383,14 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->dq_drained);
       if (pend_row != nullptr) {
-        uint4* dst = reinterpret_cast<uint4*>(pend_row);
+        // (32-byte stores: whole sectors, half as many requests as 16-byte ones)
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 o;
-          o.x = pack2<kBf16>(__uint_as_float(r[v * 8 + 0]) * mul, __uint_as_float(r[v * 8 + 1]) * mul);
-          o.y = pack2<kBf16>(__uint_as_float(r[v * 8 + 2]) * mul, __uint_as_float(r[v * 8 + 3]) * mul);
-          o.z = pack2<kBf16>(__uint_as_float(r[v * 8 + 4]) * mul, __uint_as_float(r[v * 8 + 5]) * mul);
-          o.w = pack2<kBf16>(__uint_as_float(r[v * 8 + 6]) * mul, __uint_as_float(r[v * 8 + 7]) * mul);
-          dst[v] = o;
+        for (int v = 0; v < 2; ++v) {
+          uint32_t o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            o[i] = pack2<kBf16>(__uint_as_float(r[v * 16 + 2 * i]) * mul, __uint_as_float(r[v * 16 + 2 * i + 1]) * mul);
+          st_global_v8(pend_row + v * 16, o);
         }
       }
       pend = false;
@@ -435,14 +434,17 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
           tmem_ld32(tSj + part * 32, s0);
           tmem_ld_wait();
           // one pair in four goes through the FMA pipe instead of the special-function unit
+          // (two values per instruction wherever the pipe has a packed form: the compute warps are bound
+          // by their instruction count, 16 warps on four schedulers)
+          const float2 sl2v = make_float2(sl2, sl2), nlv = make_float2(lse2_r, lse2_r);  // (the rows arrive negated, see the delta kernel)
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float x0 = fmaf(__uint_as_float(s0[i]), sl2, -lse2_r), x1 = fmaf(__uint_as_float(s0[i + 1]), sl2, -lse2_r);
+            const float2 x = __ffma2_rn(make_float2(__uint_as_float(s0[i]), __uint_as_float(s0[i + 1])), sl2v, nlv);
             if (kDqPoly && ((i >> 1) & 3) == 3) {
-              const float2 e = ex2_poly2(make_float2(x0, x1));
+              const float2 e = ex2_poly2(x);
               pr[i] = e.x, pr[i + 1] = e.y;
             } else {
-              pr[i] = ex2f(x0), pr[i + 1] = ex2f(x1);
+              pr[i] = ex2f(x.x), pr[i + 1] = ex2f(x.y);
             }
           }
         }
@@ -479,10 +481,12 @@ rswa_dq_kernel(const __grid_constant__ BwdKernelParams p, int n_q_tiles, int n_i
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl->dp_loaded);  // dP of the next tile may overwrite these columns now
+          const float2 ndv = make_float2(delta_r, delta_r);
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            dpk[i >> 1] = pack2<kBf16>(pr[i] * (__uint_as_float(d0[i]) - delta_r),
-                                       pr[i + 1] * (__uint_as_float(d0[i + 1]) - delta_r));
+            const float2 ds = __fmul2_rn(make_float2(pr[i], pr[i + 1]),
+                                         __fadd2_rn(make_float2(__uint_as_float(d0[i]), __uint_as_float(d0[i + 1])), ndv));
+            dpk[i >> 1] = pack2<kBf16>(ds.x, ds.y);
           }
         }
         // dS (16-bit) goes over the first half of the very S columns this warp has read, so no
