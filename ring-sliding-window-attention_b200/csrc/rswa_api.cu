@@ -269,7 +269,7 @@ extern "C" int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_
   if (batch <= 0 || q_len <= 0 || n_q_heads <= 0 || head_dim != kHeadDim) return -1;
   const int64_t q_len_pad = (static_cast<int64_t>(q_len) + kTile - 1) / kTile * kTile;
   // two fp32 rows per (batch, head): delta = rowsum(dO * O) and lse * log2(e), padded to whole tiles;
-  // then 256 bytes that hold the dQ kernel's work counter
+  // then 256 bytes that hold the work counters of the dQ and dK/dV kernels
   return 2 * static_cast<int64_t>(batch) * n_q_heads * q_len_pad * 4 + 256;
 }
 
@@ -306,8 +306,8 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
   float* delta = static_cast<float*>(p->workspace);
   float* lse2 = delta + static_cast<int64_t>(g.batch) * g.n_q_heads * q_len_pad;
   int* dq_counter = reinterpret_cast<int*>(lse2 + static_cast<int64_t>(g.batch) * g.n_q_heads * q_len_pad);
-  if (want_dq) {  // ahead of every kernel of this call, so that it sits in no timed interval
-    cudaError_t e = cudaMemsetAsync(dq_counter, 0, sizeof(int), static_cast<cudaStream_t>(stream_));
+  {  // both work counters, ahead of every kernel of this call, so that the reset sits in no timed interval
+    cudaError_t e = cudaMemsetAsync(dq_counter, 0, 2 * sizeof(int), static_cast<cudaStream_t>(stream_));
     if (e != cudaSuccess) {
       set_error("rswa_bwd: cudaMemsetAsync: %s", cudaGetErrorString(e));
       return RSWA_E_CUDA;
@@ -385,6 +385,7 @@ extern "C" int rswa_bwd(const rswa_bwd_params_t* p, void* stream_) {
   }
   if (p->ev_main_start) cudaEventRecord(static_cast<cudaEvent_t>(p->ev_main_start), stream);
   if (total_tiles > 0) {
+    kk.dkv_counter = dq_counter + 1;
     rc = launch_bwd(kk, g.dtype, total_tiles, stream);
     if (rc) return rc;
   }

@@ -149,7 +149,10 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int n_items) {
         if (n >= 2 && !mbar_wait<200>(&ctl->geom_free[slot], ((n >> 1) - 1) & 1, err, kErrWaitProducer)) break;
         BwdItemGeom* g = &ctl->geom[slot];
         // work item: batch row fastest, then KV head, then key tile (tiles of the first span first)
-        int idx = static_cast<int>(blockIdx.x) + n * static_cast<int>(gridDim.x);
+        // Items are handed out through a counter in global memory, in index order: a CTA that got a long
+        // item (the key tile that holds a sink token is seen by every later query tile of its sequence)
+        // or started late simply takes fewer.
+        int idx = n_work > 0 ? atomicAdd(p.dkv_counter, 1) : n_work;
         if (idx >= n_work) {
           g->valid = 0;
           mbar_arrive(&ctl->geom_full[slot]);

@@ -69,7 +69,8 @@ struct BwdKernelParams {
   const float* delta;
   long long d_sb, d_sh;
   void* dq;  // [batch, q_len, hq, 128], 16-bit, written by the dQ kernel
-  int* dq_counter;  // work counter of the dQ kernel, zeroed before its launch
+  int* dq_counter;   // work counter of the dQ kernel, zeroed before its launch
+  int* dkv_counter;  // work counter of the dK/dV kernel, likewise
   long long dq_sb, dq_st, dq_sh;
   int* status;
 };

@@ -83,7 +83,7 @@ def test_partials_merge_to_the_whole():
 
 
 def test_flop_counts_match_the_baseline_table():
-    # pairs of the BASELINE configurations (in-window only)
+    # pairs of the five benchmark configurations (in-window only)
     assert in_window_pairs([1024], 128) == 123840
     assert in_window_pairs([32768], 1000) == 32300268
     assert in_window_pairs([7204, 3978, 14070, 10318, 13142, 12634, 4190], 4096) == 209773421
