@@ -1,8 +1,8 @@
 // dK/dV kernel: the key-stationary half of the backward pass.
 //
-// One CTA owns a 128-key tile of one KV head and walks every query tile (and every query head of
-// the group) that can see it.  The products run in the transposed (key-major) form so that P and
-// dS feed the next MMA as the A operand straight from tensor memory:
+// A work item is a 128-key tile of one KV head; the CTA that takes it walks every query tile (and every
+// query head of the group) that can see it.  The products run in the transposed (key-major) form so
+// that P and dS feed the next MMA as the A operand straight from tensor memory:
 //
 //   S^T  = K Q^T          A = K   (smem, K-major)     B = Q   (smem, K-major)
 //   dP^T = V dO^T         A = V   (smem, K-major)     B = dO  (smem, K-major)
@@ -10,11 +10,18 @@
 //   dV  += P^T dO         A = P^T (TMEM)              B = dO  (smem, MN-major)
 //   dK  += dS^T Q         A = dS^T(TMEM)              B = Q   (smem, MN-major)
 //
-// dK and dV stay in TMEM for the whole CTA (summed over the query heads of the group) and are
-// written once.  dQ is the business of the query-stationary kernel (rswa_dq.cu), so nothing is
-// reduced through global memory.  P is recomputed from the saved log-sum-exp, and delta is
-// rowsum(dO * O), which is what makes a per-span backward against the FINAL out/lse exact (the
-// property the reference's per-hop backward relies on, ring_swa/ops/attn.py:63-126).
+// dK and dV stay in TMEM for the whole item (summed over the query heads of the group) and are written
+// once.  dQ is the business of the query-stationary kernel (rswa_dq.cu), so nothing is reduced through
+// global memory.  P is recomputed from the saved log-sum-exp, and delta is rowsum(dO * O), which is
+// what makes a per-span backward against the FINAL out/lse exact (the property the reference's per-hop
+// backward relies on, ring_swa/ops/attn.py:63-126).
+//
+// The kernel is persistent: one CTA per SM takes items from a counter in global memory, and every
+// pipeline (Q / dO rings, barrier phases) keeps running across item boundaries.  K and V have one buffer
+// each; they are reloaded as soon as the item's last S^T and dP^T products have been issued, i.e. while
+// its last two query tiles still run, and the item's dK / dV are read out and stored behind the first
+// exponentials of the next item.  (A one-shot CTA per key tile spent 4 100 cycles of a 34 500-cycle
+// life waiting for its first loads, and its epilogue and the launch gap were not overlapped either.)
 //
 // Pipeline: one thread issues every product, in the order  dV(i), dK(i), dP^T(i+1), S^T(i+2)  once
 // P^T | dS^T of query tile i are in tensor memory: dP^T(i+1) overwrites their columns, which issue
@@ -23,8 +30,8 @@
 // through a 3-stage ring (they are needed two tiles ahead), dO tiles through a 2-stage ring.
 // TMEM columns: [0,128) dK, [128,256) dV, [256,384) S^T, [384,512) dP^T, over which each compute
 // warp writes P^T and dS^T of the 64 query columns it has just read (P^T in the first 32 of its 64
-// columns, dS^T in the other 32), handed over in two chunks of 32 queries.  dK and dV leave through
-// shared memory as whole row segments.
+// columns, dS^T in the other 32), handed over in two chunks of 32 queries.  dK and dV leave with
+// 32-byte stores from registers (a thread owns 64 consecutive columns of one key row).
 #include "rswa_common.cuh"
 #include "tc05.cuh"
 
