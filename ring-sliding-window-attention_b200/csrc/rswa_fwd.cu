@@ -55,9 +55,13 @@ constexpr int kFwdSmemTiles = 7 * kTileBytes;  // Q_0, Q_1, output staging (one 
 constexpr int kUnits = 2;
 constexpr int kSoftmaxWarps = 8;
 #ifndef RSWA_FWD_POLY_EVERY
-#define RSWA_FWD_POLY_EVERY 4
+#define RSWA_FWD_POLY_EVERY 0
 #endif
-constexpr int kPolyEvery = RSWA_FWD_POLY_EVERY;  // 0: every exponential on the special-function unit
+// n > 0: one pair of exponentials in n goes through a cubic on the FMA pipe instead of the special-function
+// unit.  0 (every exponential on the special-function unit) measured fastest once the S row stayed in
+// registers: 1.24 ms against 1.27 (n = 4), 1.28 (3), 1.31 (2) on the benchmark workload -- the softmax warps
+// are bound by their instruction count, and the polynomial costs six times the instructions.
+constexpr int kPolyEvery = RSWA_FWD_POLY_EVERY;
 
 // flags of a unit, written by the producer ahead of the unit's loads
 enum : uint32_t {
