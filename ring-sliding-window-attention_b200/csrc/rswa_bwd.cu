@@ -258,20 +258,33 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int n_items) {
         ok = mbar_wait<kMmaPollNs>(&ctl->kv_full, nk & 1, err, kErrWaitMma);
         // one loop turn per query tile and ONE copy of each product's code; the turns -2 and -1 fill
         // the pipeline (S^T(0); then dP^T(0), S^T(1))
+        // Every barrier is PROBED one block of products ahead of where it is needed (mbarrier.try_wait once,
+        // the result looked at only after the block in between has been issued): this thread is the
+        // longest chain of the CTA, and the round trip of a probe that finds its barrier complete, as it
+        // nearly always does, otherwise stands between two blocks of products.  A probe that fails is
+        // followed by the ordinary bounded wait.
+        auto settle = [&](bool probed, uint64_t* bar, uint32_t parity) -> bool {
+          return probed || mbar_wait<kMmaPollNs>(bar, parity, err, kErrWaitMma);
+        };
         for (int it = -2; it < n_iter && ok; ++it) {
-          if (it >= 0) {
-            const int g = gbase + it;
+          const bool has_acc = it >= 0, has_dp = it + 1 >= 0 && it + 1 < n_iter, has_s = it + 2 < n_iter;
+          const int g = gbase + it, tp = g + 1, ts = g + 2;
+          const int sd = tp & 1, sq = ts % kQStages;
+          bool pr_do = false, pr_q = false, pr_sl = false;
+          if (has_acc) {
             const uint64_t dDOs = dDOm + (g & 1) * kTile16;
             const uint64_t dQs = dQm + (g % kQStages) * kTile16;
-#pragma unroll 1
+            const bool pr0 = mbar_try_wait(&ctl->pds_ready[0], g & 1);
+            const bool pr1 = mbar_try_wait(&ctl->pds_ready[1], g & 1);
+#pragma unroll  // (unrolled: the operand addresses of all 16 products are constants then, and this thread's instruction count bounds the kernel)
             for (int ch = 0; ch < 2; ++ch) {
               // P^T | dS^T arrive in two chunks: every compute warp's first 32 query columns (k-steps
               // 0, 1, 4, 5 of the 128 queries), then its other 32 (k-steps 2, 3, 6, 7)
-              ok = mbar_wait<kMmaPollNs>(&ctl->pds_ready[ch], g & 1, err, kErrWaitMma);
+              ok = settle(ch == 0 ? pr0 : pr1, &ctl->pds_ready[ch], g & 1);
               // the item's first products overwrite dK / dV: the previous item's must have been read out
               if (ok && it == 0 && ch == 0 && nk > 0) ok = mbar_wait<kMmaPollNs>(&ctl->acc_free, (nk - 1) & 1, err, kErrWaitMma);
               if (!ok) break;
-              BWD_TRC(ch == 0, g, 8);
+              if (ch == 1 && has_dp) pr_do = mbar_try_wait(&ctl->do_full[sd], (tp >> 1) & 1);
               tc_fence_after();
 #pragma unroll
               for (int kk = 0; kk < 4; ++kk) {  // dV += P^T dO
@@ -289,11 +302,14 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int n_items) {
             mma_commit(&ctl->q_free[g % kQStages]);   // (S^T of this tile, the stage's other reader, was issued before)
             if (it + 1 == n_iter) mma_commit(&ctl->done);
           }
-          if (it + 1 >= 0 && it + 1 < n_iter) {
+          if (has_dp) {
             // dP^T of the next query tile (it overwrites P^T | dS^T of this one: ordered behind their readers above)
-            const int t = gbase + it + 1, sd = t & 1;
-            ok = mbar_wait<kMmaPollNs>(&ctl->do_full[sd], (t >> 1) & 1, err, kErrWaitMma);
+            ok = settle(pr_do, &ctl->do_full[sd], (tp >> 1) & 1);
             if (!ok) break;
+            if (has_s) {
+              pr_q = mbar_try_wait(&ctl->q_full[sq], (ts / kQStages) & 1);
+              pr_sl = ts > 0 ? mbar_try_wait(&ctl->s_loaded, (ts - 1) & 1) : true;
+            }
             tc_fence_after();
             const uint64_t dDOs = dDOk + sd * kTile16;
 #pragma unroll
@@ -302,15 +318,13 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int n_items) {
               mma_ss(tB, dV + off, dDOs + off, id_kk, k > 0 ? 1u : 0u);
             }
             mma_commit(&ctl->dp_ready);
-            BWD_TRC(true, t, 9);
             // that was the item's last read of V (its last read of K, S^T of the same tile, came earlier)
             if (it + 2 == n_iter) mma_commit(&ctl->kv_free);
           }
-          if (it + 2 < n_iter) {
+          if (has_s) {
             // S^T of the query tile after next, once the compute warps hold the tile before it in registers
-            const int t = gbase + it + 2, sq = t % kQStages;
-            ok = mbar_wait<kMmaPollNs>(&ctl->q_full[sq], (t / kQStages) & 1, err, kErrWaitMma);
-            if (ok && t > 0) ok = mbar_wait<kMmaPollNs>(&ctl->s_loaded, (t - 1) & 1, err, kErrWaitMma);
+            ok = settle(pr_q, &ctl->q_full[sq], (ts / kQStages) & 1);
+            if (ok && ts > 0) ok = settle(pr_sl, &ctl->s_loaded, (ts - 1) & 1);
             if (!ok) break;
             tc_fence_after();
             const uint64_t dQs = dQk + sq * kTile16;
@@ -320,7 +334,6 @@ rswa_bwd_kernel(const __grid_constant__ BwdKernelParams p, int n_items) {
               mma_ss(tS, dK + off, dQs + off, id_kk, k > 0 ? 1u : 0u);
             }
             mma_commit(&ctl->s_ready);
-            BWD_TRC(true, t, 10);
           }
         }
         gbase += n_iter;
