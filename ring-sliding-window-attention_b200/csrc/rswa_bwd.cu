@@ -52,9 +52,9 @@ constexpr int kBwdTmemCols = 512;
 constexpr int kComputeThreads = 256;
 constexpr int kQStages = 3;
 #ifndef RSWA_BWD_POLY
-#define RSWA_BWD_POLY 0
+#define RSWA_BWD_POLY 1
 #endif
-constexpr bool kBwdPoly = RSWA_BWD_POLY != 0;  // a quarter of the exponentials on the FMA pipe (off: measured 0.7 % slower here; the dQ kernel keeps it)
+constexpr bool kBwdPoly = RSWA_BWD_POLY != 0;  // a quarter of the exponentials on the FMA pipe (worth 0.6 % here: two compute warps per scheduler need 1 024 cycles of the special-function unit per query tile)
 
 // what every role needs to know about a work item (one key tile of one KV head), filled by the producer
 struct BwdItemGeom {
