@@ -100,7 +100,10 @@ def packed_pairs(seq_lens, W: int, n_sink: int) -> int:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region."""
+    """nvidia-smi clocks and throttle reasons during the timed region, every 20 ms: the figures reported are
+    those of the samples taken while the device-resident region ran (`mark()` at its start and end), i.e.
+    under load -- a board that idles at its maximum clock drops by a fifth within a few hundred
+    milliseconds of these kernels (power cap)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -109,11 +112,12 @@ class ClockSampler:
         self.n = n_gpus
         self.rows = []
         self.proc = None
+        self.marks = []
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
@@ -121,7 +125,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append(line.strip())
+            self.rows.append((time.monotonic(), line.strip()))
+
+    def mark(self):
+        self.marks.append(time.monotonic())
 
     def stop(self):
         if self.proc is None:
@@ -132,7 +139,11 @@ class ClockSampler:
         except Exception:
             pass
         sm, smax, reasons, power = [], [], set(), []
-        for r in self.rows:
+        rows = self.rows
+        if len(self.marks) >= 2:  # the samples under load, if there are any (a short region may see none)
+            inside = [r for r in rows if self.marks[0] <= r[0] <= self.marks[1] + 0.02]
+            rows = inside or rows
+        for _t, r in rows:
             f = [x.strip() for x in r.split(",")]
             if len(f) < 8 or not f[0].isdigit() or int(f[0]) >= self.n:
                 continue
@@ -144,7 +155,8 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons),
+                "sampled": "during the device-resident timed region" if len(self.marks) >= 2 and rows is not self.rows else "whole run"}
 
 
 def measured_peaks():
@@ -460,11 +472,15 @@ def main():
     launches0 = K.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
+    if sampler:
+        sampler.mark()
     e0.record()
     for _ in range(args.steps):
         step(q, k, v, do)
     e1.record()
     sync_all()
+    if sampler:
+        sampler.mark()
     ms = e0.elapsed_time(e1)
     launches = K.launch_count - launches0
     lib = _C.lib()
@@ -638,6 +654,8 @@ def main():
             "data": "synthetic", "config": workload_config(args, wl, n),
             "tflops_per_gpu_in_window": 14 * D * Hq * pairs_total / n / (ms_step * 1e-3) / 1e12,
             "frac_of_bf16_peak": 14 * D * Hq * pairs_total / n / (ms_step * 1e-3) / 1e12 / peak_tf,
+            "bf16_peak_used": {"tflops": peak_tf, "which": peak_name,
+                               "frac_of_burst_peak": 14 * D * Hq * pairs_total / n / (ms_step * 1e-3) / 1e12 / measured_peaks()[0]},
             "roofline": {"kernel": "rswa_bwd_kernel (dK/dV)", "bound": "tensor", "achieved": ach_bwd, "peak": peak_tf,
                          "unit": "TFLOP/s", "frac": ach_bwd / peak_tf, "traffic": TRAFFIC_DKDV_CFG2 if args.workload == "cfg2" and n == 1 else None,
                          "peak_source": f"{peak_kind} {peak_name}", "ms_per_launch": bwd_ms,
