@@ -30,7 +30,9 @@ __device__ __forceinline__ uint32_t pack2f(float lo, float hi) {
   }
 }
 
-// Half a warp per (b, t, h) row of 128 elements (16 bytes per lane and tensor).  Writes
+// A warp takes 32 consecutive tokens of one (batch row, head): half a warp per 128-element row (16 bytes
+// per lane and tensor), eight rows in flight per lane pair, and the 32 results leave as ONE 128-byte
+// segment of each output row (one token per lane) instead of 32 scattered words.  Writes
 // -delta = -rowsum(dO * O) and -lse2 = -lse * log2(e) into rows padded to whole 128-query tiles; the
 // padding gets -delta = 0 and -lse2 = -inf so that P = exp2(s - lse2) vanishes there.
 template <bool kBf16>
@@ -39,37 +41,60 @@ __global__ void delta_kernel(const uint16_t* __restrict__ out, long long o_sb, l
                              const float* __restrict__ lse, long long l_sb, long long l_sh,
                              float* __restrict__ delta, float* __restrict__ lse2, int batch, int q_len, int hq,
                              int q_len_pad) {
-  const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-  const int sub = threadIdx.x & 15;
-  const long long n_rows = static_cast<long long>(batch) * q_len_pad * hq;
-  if (row >= n_rows) return;
-  const int h = row % hq;
-  const long long bt = row / hq;
-  const int t = bt % q_len_pad;
-  const int b = bt / q_len_pad;
-  float s = 0.f;
-  if (t < q_len) {
-    const uint4 a = *reinterpret_cast<const uint4*>(out + b * o_sb + t * o_st + h * o_sh + sub * 8);
-    const uint4 d = *reinterpret_cast<const uint4*>(dout + b * d_sb + t * d_st + h * d_sh + sub * 8);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;  // warp task
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & 15, hi = lane >> 4;
+  const int t_blocks = q_len_pad >> 5;  // q_len_pad is a multiple of 128
+  const long long n_tasks = static_cast<long long>(batch) * hq * t_blocks;
+  if (wid >= n_tasks) return;
+  const int tb = wid % t_blocks;       // token block fastest: neighbouring warps read neighbouring tokens
+  const long long bh = wid / t_blocks;
+  const int h = bh % hq;
+  const int b = bh / hq;
+  const int t0 = tb * 32;
+  const uint16_t* po = out + b * o_sb + h * o_sh + sub * 8;
+  const uint16_t* pd = dout + b * d_sb + h * d_sh + sub * 8;
+  float mine = 0.f;  // the sum of the token this lane will write (t0 + lane)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = unpack2<kBf16>(aw[i]), y = unpack2<kBf16>(dw[i]);
-      s += x.x * y.x + x.y * y.y;
+  for (int blk = 0; blk < 2; ++blk) {  // 16 tokens per block: 8 loads of each tensor in flight per lane
+    uint4 a[8], d[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = t0 + blk * 16 + 2 * i + hi;
+      if (t < q_len) {
+        a[i] = *reinterpret_cast<const uint4*>(po + t * o_st);
+        d[i] = *reinterpret_cast<const uint4*>(pd + t * d_st);
+      } else {
+        a[i] = make_uint4(0, 0, 0, 0);
+        d[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t aw[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, dw[4] = {d[i].x, d[i].y, d[i].z, d[i].w};
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = unpack2<kBf16>(aw[j]), y = unpack2<kBf16>(dw[j]);
+        s += x.x * y.x + x.y * y.y;
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      // lanes 0-15 hold the sum of token t0 + 16 blk + 2 i, lanes 16-31 that of the next one
+      const float lo_sum = __shfl_sync(0xffffffffu, s, 0), hi_sum = __shfl_sync(0xffffffffu, s, 16);
+      if (lane == blk * 16 + 2 * i) mine = lo_sum;
+      if (lane == blk * 16 + 2 * i + 1) mine = hi_sum;
     }
   }
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (sub == 0) {
-    const long long idx = (static_cast<long long>(b) * hq + h) * q_len_pad + t;
-    // both rows are stored NEGATED: the backward kernels only ever add them (s * scale - lse2, dP - delta),
-    // once per score, and their inner loops are bound by instruction count
-    delta[idx] = -s;
-    // (a row that saw no key at all has lse = -inf: it gets -inf like the padding, so that its P vanishes
-    // whatever its scores are, -inf included, instead of turning into inf - inf)
-    const float l = t < q_len ? lse[b * l_sb + h * l_sh + t] : -INFINITY;
-    lse2[idx] = l > -INFINITY ? l * -1.4426950408889634f : -INFINITY;
-  }
+  const int t = t0 + lane;
+  const long long idx = (static_cast<long long>(b) * hq + h) * q_len_pad + t;
+  // both rows are stored NEGATED: the backward kernels only ever add them (s * scale - lse2, dP - delta),
+  // once per score, and their inner loops are bound by instruction count
+  delta[idx] = -mine;
+  // (a row that saw no key at all has lse = -inf: it gets -inf like the padding, so that its P vanishes
+  // whatever its scores are, -inf included, instead of turning into inf - inf)
+  const float l = t < q_len ? lse[b * l_sb + h * l_sh + t] : -INFINITY;
+  lse2[idx] = l > -INFINITY ? l * -1.4426950408889634f : -INFINITY;
 }
 
 // LSE merge.  16 threads per (b, t, h) row, each 8 elements (16 bytes) of both inputs.
@@ -236,9 +261,9 @@ int check_launch(const char* what) {
 
 int launch_delta(const rswa_bwd_params_t& p, float* delta, float* lse2, int q_len_pad, cudaStream_t stream) {
   const rswa_geom_t& g = p.g;
-  const long long rows = static_cast<long long>(g.batch) * q_len_pad * g.n_q_heads;
+  const long long tasks = static_cast<long long>(g.batch) * g.n_q_heads * (q_len_pad / 32);  // one warp each
   const int threads = 256;
-  const long long blocks = (rows * 16 + threads - 1) / threads;
+  const long long blocks = (tasks * 32 + threads - 1) / threads;
   auto kern = g.dtype == RSWA_DTYPE_BF16 ? delta_kernel<true> : delta_kernel<false>;
   kern<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
       static_cast<const uint16_t*>(p.out), p.o_stride_b, p.o_stride_t, p.o_stride_h,
