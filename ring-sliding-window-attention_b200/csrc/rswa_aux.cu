@@ -97,48 +97,70 @@ __global__ void delta_kernel(const uint16_t* __restrict__ out, long long o_sb, l
   lse2[idx] = l > -INFINITY ? l * -1.4426950408889634f : -INFINITY;
 }
 
-// LSE merge.  16 threads per (b, t, h) row, each 8 elements (16 bytes) of both inputs.
+// LSE merge.  A warp takes 32 consecutive tokens of one (batch row, head): lane i reads the two lse values
+// of token i (one 128-byte segment each), forms the weights and writes the merged lse (one segment); the
+// rows go through half a warp each (16 bytes per lane and tensor), eight rows of each input in flight
+// per lane pair, their weights fetched from the owning lane with a shuffle.  In place (o == o_a) is allowed:
+// a row is read and written by the same lanes.
 template <bool kBf16>
-__global__ void merge_kernel(const rswa_merge_params_t p, long long n_vec) {
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= n_vec) return;
-  const unsigned live = __activemask();
-  const int c = i & 15;
-  const long long row = i >> 4;
-  const int h = row % p.n_heads;
-  const long long bt = row / p.n_heads;
-  const int t = bt % p.q_len;
-  const long long b = bt / p.q_len;
-  const long long li = b * p.lse_stride_b + h * p.lse_stride_h + t;
-  const float la = p.lse_a[li], lb = p.lse_b[li];
-  const float mx = fmaxf(la, lb);
-  float wa, wb, l;
-  if (mx == -INFINITY) {
-    wa = wb = 0.f;
-    l = -INFINITY;
-  } else {
-    const float ea = __expf(la - mx), eb = __expf(lb - mx);
-    const float inv = 1.f / (ea + eb);
-    wa = ea * inv;
-    wb = eb * inv;
-    l = mx + __logf(ea + eb);
+__global__ void merge_kernel(const rswa_merge_params_t p, long long n_tasks) {
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (wid >= n_tasks) return;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane & 15, hi = lane >> 4;
+  const int t_blocks = (p.q_len + 31) >> 5;
+  const int tb = wid % t_blocks;
+  const long long bh = wid / t_blocks;
+  const int h = bh % p.n_heads;
+  const long long b = bh / p.n_heads;
+  const int t0 = tb * 32;
+  const int tl = t0 + lane;
+  const long long li = b * p.lse_stride_b + h * p.lse_stride_h + tl;
+  float wa = 0.f, wb = 0.f, l = -INFINITY;
+  if (tl < p.q_len) {
+    const float la = p.lse_a[li], lb = p.lse_b[li];
+    const float mx = fmaxf(la, lb);
+    if (mx != -INFINITY) {
+      const float ea = __expf(la - mx), eb = __expf(lb - mx);
+      const float inv = 1.f / (ea + eb);
+      wa = ea * inv;
+      wb = eb * inv;
+      l = mx + __logf(ea + eb);
+    }
   }
-  const uint4 a = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.o_a) + b * p.oa_stride_b +
-                                                  t * p.oa_stride_t + h * p.oa_stride_h + c * 8);
-  const uint4 bb = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.o_b) + b * p.ob_stride_b +
-                                                   t * p.ob_stride_t + h * p.ob_stride_h + c * 8);
-  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {bb.x, bb.y, bb.z, bb.w};
-  uint32_t ow[4];
+  const uint16_t* pa = static_cast<const uint16_t*>(p.o_a) + b * p.oa_stride_b + h * p.oa_stride_h + sub * 8;
+  const uint16_t* pb = static_cast<const uint16_t*>(p.o_b) + b * p.ob_stride_b + h * p.ob_stride_h + sub * 8;
+  uint16_t* po = static_cast<uint16_t*>(p.o) + b * p.o_stride_b + h * p.o_stride_h + sub * 8;
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const float2 fa = unpack2<kBf16>(aw[k]), fb = unpack2<kBf16>(bw[k]);
-    ow[k] = pack2f<kBf16>(fa.x * wa + fb.x * wb, fa.y * wa + fb.y * wb);
+  for (int blk = 0; blk < 2; ++blk) {
+    uint4 va[8], vb[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int t = t0 + blk * 16 + 2 * i + hi;
+      if (t < p.q_len) {
+        va[i] = *reinterpret_cast<const uint4*>(pa + t * p.oa_stride_t);
+        vb[i] = *reinterpret_cast<const uint4*>(pb + t * p.ob_stride_t);
+      } else {
+        va[i] = make_uint4(0, 0, 0, 0);
+        vb[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int src = blk * 16 + 2 * i + hi;  // the lane that owns this row's token
+      const float xa = __shfl_sync(0xffffffffu, wa, src), xb = __shfl_sync(0xffffffffu, wb, src);
+      const uint32_t aw[4] = {va[i].x, va[i].y, va[i].z, va[i].w}, bw[4] = {vb[i].x, vb[i].y, vb[i].z, vb[i].w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 fa = unpack2<kBf16>(aw[k]), fb = unpack2<kBf16>(bw[k]);
+        ow[k] = pack2f<kBf16>(fa.x * xa + fb.x * xb, fa.y * xa + fb.y * xb);
+      }
+      const int t = t0 + src;
+      if (t < p.q_len) *reinterpret_cast<uint4*>(po + t * p.o_stride_t) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
   }
-  *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o) + b * p.o_stride_b + t * p.o_stride_t +
-                            h * p.o_stride_h + c * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-  // all 16 threads of the row have read la/lb (in place is allowed); one writes
-  __syncwarp(live);
-  if (c == 0) p.lse[li] = l;
+  if (tl < p.q_len) p.lse[li] = l;
 }
 
 // In-place merge into a float accumulator (and a float or double lse), the precision the reference
@@ -302,11 +324,12 @@ extern "C" int rswa_merge(const rswa_merge_params_t* p, void* stream) {
     set_error("rswa_merge: pointers must be 16-byte aligned");
     return RSWA_E_ARG;
   }
-  const long long n_vec = static_cast<long long>(p->batch) * p->q_len * p->n_heads * 16;
+  const long long n_tasks = static_cast<long long>(p->batch) * p->n_heads * ((p->q_len + 31) / 32);  // one warp each
+  const long long n_vec = n_tasks * 32;
   const int threads = 256;
   auto kern = p->dtype == RSWA_DTYPE_BF16 ? merge_kernel<true> : merge_kernel<false>;
   kern<<<static_cast<unsigned>((n_vec + threads - 1) / threads), threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      *p, n_vec);
+      *p, n_tasks);
   return check_launch("rswa_merge");
 }
 
