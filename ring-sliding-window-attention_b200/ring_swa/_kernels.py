@@ -142,7 +142,9 @@ def _check4(name: str, t: torch.Tensor) -> None:
 
 
 def _stream() -> C.c_void_p:
-    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of torch's current stream without building a Stream object: this runs a dozen times per
+    # step and the Python-level getter costs ~15 us a call
+    return C.c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _fill_geom(g: _C.Geom, q: torch.Tensor, spans: Sequence[KVSpan], window: int, n_sink: int, scale: float,

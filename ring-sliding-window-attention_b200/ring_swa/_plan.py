@@ -8,6 +8,11 @@ rank r needs the keys at global positions [max(seq_start, r*S - W), r*S), i.e. t
 min(S, ...) tokens of ranks r-1, r-2, ..., plus (StreamingLLM) the first n_sink tokens of the
 sequence that crosses its left edge, sent by the rank that owns them
 (ring_swa/streaming_llm/nonvarlen.py:48-55 broadcasts them from group rank 0).
+
+Chunks need not be equal: the reference assumes the same number of tokens on every rank
+(ring_swa/sliding_window/varlen.py:56-59, its FIXME); with `chunk_lens` (one length per group rank)
+rank r owns the positions [bounds[r], bounds[r+1]) of the packed token axis, bounds being the
+running sum, and everything below works on those bounds.
 """
 from __future__ import annotations
 
@@ -54,9 +59,10 @@ class SinkSend:
 class RingPlan:
     cp: int
     rank: int
-    seq_per_rank: int
+    seq_per_rank: int         # tokens on THIS rank
     window: int
     n_sink: int
+    pos_start: int = 0        # global position of this rank's first token
     halo_recv: List[HaloRecv] = field(default_factory=list)
     halo_send: List[HaloSend] = field(default_factory=list)
     sink_recv: List[SinkRecv] = field(default_factory=list)   # ascending position, one per owning rank
@@ -66,7 +72,7 @@ class RingPlan:
 
     @property
     def q_pos_start(self) -> int:
-        return self.rank * self.seq_per_rank
+        return self.pos_start
 
     @property
     def n_tiles(self) -> int:
@@ -82,7 +88,20 @@ def seq_start_of(pos: int, cu: Optional[Sequence[int]]) -> int:
     return int(cu[i])
 
 
-def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv], List[SinkRecv]]:
+def chunk_bounds(cp: int, S: int, chunk_lens: Optional[Sequence[int]]) -> List[int]:
+    """Global position of every rank's first token, plus the total: cp + 1 ascending numbers."""
+    if chunk_lens is None:
+        return [r * S for r in range(cp + 1)]
+    lens = [int(x) for x in chunk_lens]
+    if len(lens) != cp or any(x <= 0 for x in lens):
+        raise ValueError(f"chunk lengths must be {cp} positive numbers, one per rank of the group: {lens}")
+    bounds = [0]
+    for x in lens:
+        bounds.append(bounds[-1] + x)
+    return bounds
+
+
+def _needs(r: int, bounds: Sequence[int], W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv], List[SinkRecv]]:
     """What rank r must receive: (lowest needed window position, halos, sink).
 
     The sink tokens of the sequence that crosses the rank's left edge always travel as their own
@@ -90,7 +109,7 @@ def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv]
     of that sequence needs them, also the ones that otherwise see local keys only and run before
     the halo has arrived.  The halo then starts behind the sink tokens, so the two never overlap.
     """
-    left = r * S
+    left = bounds[r]
     s_cross = seq_start_of(left, cu)
     lo = max(s_cross, left - W, 0)
     sink: List[SinkRecv] = []
@@ -98,15 +117,15 @@ def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv]
         end = min(s_cross + n_sink, left)
         a = s_cross
         while a < end:  # one piece per rank that owns some of [s_cross, end)
-            owner = a // S
-            b = min(end, (owner + 1) * S)
+            owner = bisect.bisect_right(bounds, a) - 1
+            b = min(end, bounds[owner + 1])
             sink.append(SinkRecv(owner=owner, pos_start=a, n=b - a))
             a = b
         lo = max(lo, end)
     halos: List[HaloRecv] = []
     h = 1
     while r - h >= 0:
-        a, b = (r - h) * S, (r - h + 1) * S
+        a, b = bounds[r - h], bounds[r - h + 1]
         if b <= lo:
             break
         start = max(lo, a)
@@ -115,22 +134,27 @@ def _needs(r: int, S: int, W: int, n_sink: int, cu) -> Tuple[int, List[HaloRecv]
     return lo, halos, sink
 
 
-def make_plan(cp: int, rank: int, S: int, W: int, n_sink: int, cu: Optional[Sequence[int]]) -> RingPlan:
-    """Plan for `rank`; every rank derives the matching sends from the other ranks' needs."""
+def make_plan(cp: int, rank: int, S: int, W: int, n_sink: int, cu: Optional[Sequence[int]],
+              chunk_lens: Optional[Sequence[int]] = None) -> RingPlan:
+    """Plan for `rank`; every rank derives the matching sends from the other ranks' needs.
+    `S` is the number of tokens on this rank; `chunk_lens` (all ranks' lengths) when they differ."""
     if cp < 1 or not (0 <= rank < cp):
         raise ValueError(f"invalid context-parallel geometry: cp_size={cp}, cp_local_rank={rank}")
     if S <= 0 or W < 0 or n_sink < 0:
         raise ValueError("sequence length per rank must be positive, window and n_sink non-negative")
-    plan = RingPlan(cp=cp, rank=rank, seq_per_rank=S, window=W, n_sink=n_sink)
-    lo, plan.halo_recv, plan.sink_recv = _needs(rank, S, W, n_sink, cu)
+    bounds = chunk_bounds(cp, S, chunk_lens)
+    if bounds[rank + 1] - bounds[rank] != S:
+        raise ValueError(f"rank {rank} holds {S} tokens but its chunk length is given as {bounds[rank + 1] - bounds[rank]}")
+    plan = RingPlan(cp=cp, rank=rank, seq_per_rank=S, window=W, n_sink=n_sink, pos_start=bounds[rank])
+    lo, plan.halo_recv, plan.sink_recv = _needs(rank, bounds, W, n_sink, cu)
     for r in range(rank + 1, cp):
-        _, halos, sink = _needs(r, S, W, n_sink, cu)
+        _, halos, sink = _needs(r, bounds, W, n_sink, cu)
         for hr in halos:
             if hr.src == rank:
                 plan.halo_send.append(HaloSend(hop=hr.hop, dst=r, length=hr.length))
         for piece in sink:
             if piece.owner == rank:
-                plan.sink_send.append(SinkSend(dst=r, offset=piece.pos_start - rank * S, n=piece.n))
+                plan.sink_send.append(SinkSend(dst=r, offset=piece.pos_start - bounds[rank], n=piece.n))
     if plan.halo_recv:
         # local query a (position rank*S + a) reaches below the chunk iff a < W
         plan.halo_tile_end = min(plan.n_tiles, (min(W, S) + TILE - 1) // TILE)

@@ -105,6 +105,7 @@ class RingCtx:
     rank: int
     prev_global: Optional[int]
     next_global: Optional[int]
+    chunk_lens: Optional[tuple] = None   # tokens per group rank where the chunks differ in length
 
     def global_rank(self, group_rank: int) -> int:
         if group_rank == self.rank + 1 and self.next_global is not None:
@@ -150,7 +151,7 @@ class RingAttn(torch.autograd.Function):
             v4 = v4.contiguous()
             k4 = k4.contiguous()
         B, S, Hq, D = q4.shape
-        plan = make_plan(ring.cp, ring.rank, S, window, n_sink, cu_host)
+        plan = make_plan(ring.cp, ring.rank, S, window, n_sink, cu_host, ring.chunk_lens)
         if 1 + len(plan.halo_recv) + len(plan.sink_recv) > _C.RSWA_MAX_SPANS:
             raise ValueError("window reaches over more ranks than one call supports "
                              f"({len(plan.halo_recv)} hops)")
@@ -172,7 +173,8 @@ class RingAttn(torch.autograd.Function):
         # communication kernel runs next to the attention kernels), torch.distributed messages otherwise.
         link = None
         if ring.cp > 1 and q4.is_cuda and _peer.wanted():
-            link = _peer.link_for(ring.group, q4.device, ring.cp, S, window, B, k4.shape[2], D)
+            lens = ring.chunk_lens or (S,)
+            link = _peer.link_for(ring.group, q4.device, ring.cp, max(lens), window, B, k4.shape[2], D, min(lens))
         halo_spans = []
         halo_shape = lambda r: (2, B, r.length) + tuple(k4.shape[2:])  # noqa: E731
         if link is not None:
@@ -362,7 +364,7 @@ class RingAttn(torch.autograd.Function):
         return dq4, dk4, dv4, None, None, None, None, None, None
 
 
-def ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank) -> RingCtx:
+def ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank, chunk_lens=None) -> RingCtx:
     """Argument defaulting of ring_swa/sliding_window/nonvarlen.py:388-395."""
     if cp_group is None:
         return RingCtx(None, 1, 0, None, None)
@@ -370,7 +372,8 @@ def ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_glob
         cp_size = dist.get_world_size(cp_group)
     if cp_local_rank is None:
         cp_local_rank = dist.get_rank(group=cp_group)
-    return RingCtx(cp_group, int(cp_size), int(cp_local_rank), cp_prev_global_rank, cp_next_global_rank)
+    lens = None if chunk_lens is None else tuple(int(x) for x in chunk_lens)
+    return RingCtx(cp_group, int(cp_size), int(cp_local_rank), cp_prev_global_rank, cp_next_global_rank, lens)
 
 
 def attention(q, k, v, window_size: int, n_sink: int, softmax_scale: Optional[float],

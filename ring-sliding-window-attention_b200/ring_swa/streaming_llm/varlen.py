@@ -1,5 +1,5 @@
 """ring_streaming_llm_attn_varlen: same signature as ring_swa/streaming_llm/varlen.py:476-488."""
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 from torch.distributed import ProcessGroup
@@ -22,6 +22,7 @@ def ring_streaming_llm_attn_varlen(
     softmax_scale: Optional[float] = None,
     *,
     num_sink_tokens: int = 1,
+    cp_chunk_lens: Optional[Sequence[int]] = None,
 ) -> torch.Tensor:
     """Ring StreamingLLM attention over packed variable-length sequences.
 
@@ -30,7 +31,8 @@ def ring_streaming_llm_attn_varlen(
     documents the assumption that every sequence starts with the same sink content
     (ring_swa/streaming_llm/varlen.py:50-63, 476-488); under that assumption both are the same function,
     and the sink gradient lands on each sequence's own first token as in the reference (:454-467).
+    `cp_chunk_lens`: chunks of different lengths per rank, as in ring_sliding_window_attn_varlen.
     """
-    cu_seqlens, cu_host = _varlen_prologue(q, k, v, cu_seqlens, cp_size)
-    ring = ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank)
+    cu_seqlens, cu_host = _varlen_prologue(q, k, v, cu_seqlens, cp_size, cp_chunk_lens)
+    ring = ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank, cp_chunk_lens)
     return attention(q, k, v, window_size, num_sink_tokens, softmax_scale, cu_seqlens, cu_host, ring)

@@ -72,7 +72,11 @@ def run_rank(rank, ws, port, jobs, outdir, device="cpu"):
         q, k, v, do = make_inputs(job["seed"], job["T"], job["hq"], job["hkv"], job["d"], job["bf16_grid"],
                                   None if varlen else job["B"], job.get("sink_rows"))
         S = job["T"] // ws
-        sl = (slice(rank * S, (rank + 1) * S),) if varlen else (slice(None), slice(rank * S, (rank + 1) * S))
+        a, b = rank * S, (rank + 1) * S
+        if job.get("chunk_lens"):   # chunks of different lengths (varlen functions only)
+            a = sum(job["chunk_lens"][:rank])
+            b = a + job["chunk_lens"][rank]
+        sl = (slice(a, b),) if varlen else (slice(None), slice(a, b))
         dt = job.get("dtype", torch.float32)
         ql, kl, vl, dol = (x[sl].clone().to(device=device, dtype=dt) for x in (q, k, v, do))
         for x in (ql, kl, vl):
@@ -80,6 +84,8 @@ def run_rank(rank, ws, port, jobs, outdir, device="cpu"):
         kw = dict(window_size=job["W"], cp_group=dist.group.WORLD, cp_size=ws, cp_local_rank=rank)
         if varlen:
             kw["cu_seqlens"] = torch.tensor(job["cu"], dtype=torch.int32, device=device)
+        if job.get("chunk_lens"):
+            kw["cp_chunk_lens"] = job["chunk_lens"]
         if job.get("n_sink", 1) != 1 and "streaming" in job["fn"]:
             kw["num_sink_tokens"] = job["n_sink"]
         out = fn(ql, kl, vl, **kw)

@@ -130,6 +130,54 @@ def test_plan_covers_every_visible_key_exactly_once():
                 assert _visible_keys(p, cu, W, n_sink) <= near
 
 
+def test_unequal_chunks_cover_every_visible_key_and_sends_mirror_receives():
+    """Chunks of different lengths per rank (cp_chunk_lens of the varlen functions; the reference assumes
+    equal ones, ring_swa/sliding_window/varlen.py:56-59): the same brute-force coverage check on the
+    chunk bounds, and every receive of one rank is some other rank's send of the same tokens."""
+    import random
+    rng = random.Random(11)
+    for trial in range(1500):
+        cp = rng.randint(1, 5)
+        lens = [rng.choice([1, 2, 3, 5, 8, 13]) for _ in range(cp)]
+        bounds = [sum(lens[:i]) for i in range(cp + 1)]
+        T = bounds[-1]
+        W = rng.randint(0, T + 2)
+        n_sink = rng.choice([0, 1, 2, 3, 5])
+        cuts = sorted(rng.sample(range(1, T), min(T - 1, rng.randint(0, 4)))) if T > 1 else []
+        cu = [0] + cuts + [T]
+        plans = [make_plan(cp, r, lens[r], W, n_sink, cu, lens) for r in range(cp)]
+        for r, plan in enumerate(plans):
+            assert plan.q_pos_start == bounds[r] and plan.seq_per_rank == lens[r]
+            have = list(range(bounds[r], bounds[r + 1]))
+            for h in plan.halo_recv:
+                assert h.src == r - h.hop and bounds[h.src] <= h.pos_start and h.pos_start + h.length == bounds[h.src + 1]
+                have += range(h.pos_start, h.pos_start + h.length)
+                assert any(s.dst == r and s.hop == h.hop and s.length == h.length for s in plans[h.src].halo_send)
+            for sr in plan.sink_recv:
+                assert bounds[sr.owner] <= sr.pos_start and sr.pos_start + sr.n <= bounds[sr.owner + 1]
+                have += range(sr.pos_start, sr.pos_start + sr.n)
+                assert any(s.dst == r and s.offset == sr.pos_start - bounds[sr.owner] and s.n == sr.n
+                           for s in plans[sr.owner].sink_send)
+            assert sum(len(q.halo_send) for q in plans) == sum(len(q.halo_recv) for q in plans)
+            assert sum(len(q.sink_send) for q in plans) == sum(len(q.sink_recv) for q in plans)
+            assert len(have) == len(set(have)), (lens, r, W, n_sink, cu)
+            need = set()
+            for p_ in range(bounds[r], bounds[r + 1]):
+                need |= _visible_keys(p_, cu, W, n_sink)
+            assert need <= set(have), (lens, r, W, n_sink, cu, sorted(need - set(have)))
+            near = set(range(bounds[r], bounds[r + 1]))
+            for sr in plan.sink_recv:
+                near |= set(range(sr.pos_start, sr.pos_start + sr.n))
+            for p_ in range(bounds[r] + plan.halo_tile_end * 128, bounds[r + 1]):
+                assert _visible_keys(p_, cu, W, n_sink) <= near
+    with pytest.raises(ValueError):
+        make_plan(3, 1, 5, 4, 0, None, [5, 6, 5])      # this rank's length contradicts the list
+    with pytest.raises(ValueError):
+        make_plan(3, 1, 5, 4, 0, None, [5, 5])         # one length per rank
+    with pytest.raises(ValueError):
+        make_plan(3, 1, 5, 4, 0, None, [5, 5, 0])      # empty chunks are not supported
+
+
 def test_rejects_bad_geometry():
     with pytest.raises(ValueError):
         make_plan(4, 4, 16, 5, 0, None)

@@ -47,7 +47,7 @@ def test_ring_matches_reference_pins_cp4():
     _assert_small(res, jobs, TOL)
 
 
-def _dense_job(fn, T, B, hq, hkv, d, W, seed, cu=None, n_sink=0):
+def _dense_job(fn, T, B, hq, hkv, d, W, seed, cu=None, n_sink=0, chunk_lens=None):
     varlen = cu is not None
     sink_rows = None
     q, k, v, do = make_inputs(seed, T, hq, hkv, d, False, None if varlen else B, sink_rows)
@@ -57,7 +57,7 @@ def _dense_job(fn, T, B, hq, hkv, d, W, seed, cu=None, n_sink=0):
     if varlen:
         exp = {k_: v_.squeeze(0) for k_, v_ in exp.items()}
     return dict(fn=fn, T=T, B=B, hq=hq, hkv=hkv, d=d, W=W, seed=seed, cu=cu, n_sink=n_sink, bf16_grid=False,
-                expect={k_: v_.float().numpy() for k_, v_ in exp.items()})
+                chunk_lens=chunk_lens, expect={k_: v_.float().numpy() for k_, v_ in exp.items()})
 
 
 @pytest.mark.timeout(600)
@@ -97,4 +97,22 @@ def test_sink_tokens_on_two_ranks_cp3():
         _dense_job("ring_streaming_llm_attn", 12, 1, 2, 1, 8, 2, 33, n_sink=9),   # more sink tokens than a chunk holds
     ]
     res = _spawn(3, 29751, jobs)
+    _assert_small(res, jobs, TOL)
+
+
+@pytest.mark.timeout(600)
+def test_chunks_of_different_lengths_cp3():
+    """cp_chunk_lens: the packed token axis cut into unequal shares (at sequence boundaries, inside
+    sequences, a chunk shorter than the window so that the halo comes from two ranks, a one-token
+    chunk), against the dense oracle on the global sequence."""
+    V, SV = "ring_sliding_window_attn_varlen", "ring_streaming_llm_attn_varlen"
+    jobs = [
+        _dense_job(V, 600, None, 2, 1, 8, 70, 41, cu=[0, 150, 420, 600], chunk_lens=[150, 270, 180]),   # cut at sequence starts
+        _dense_job(V, 600, None, 2, 2, 8, 90, 42, cu=[0, 100, 600], chunk_lens=[310, 40, 250]),        # W > middle chunk: two hops
+        _dense_job(V, 600, None, 2, 1, 8, 700, 43, cu=[0, 600], chunk_lens=[1, 399, 200]),            # W >= T, one-token chunk
+        _dense_job(V, 600, None, 2, 1, 8, 130, 44, cu=[0, 290, 291, 600], chunk_lens=[200, 100, 300]),
+        _dense_job(SV, 600, None, 2, 1, 8, 50, 45, cu=[0, 130, 500, 600], n_sink=1, chunk_lens=[128, 272, 200]),
+        _dense_job(SV, 600, None, 2, 2, 8, 60, 46, cu=[0, 199, 600], n_sink=3, chunk_lens=[200, 150, 250]),   # sink pieces on two ranks
+    ]
+    res = _spawn(3, 29761, jobs)
     _assert_small(res, jobs, TOL)
