@@ -133,12 +133,14 @@ typedef struct rswa_bwd_params {
   int64_t workspace_bytes;
   int32_t flags;
   int32_t* status;
-  /* Optional profiling hooks: events from rswa_event_create(), recorded on the stream right
-   * before and right after the two tensor-core kernels (the delta kernel excluded).
-   * NULL to skip. */
+  /* Optional hooks: events from rswa_event_create(), recorded on the stream right before and
+   * right after the two tensor-core kernels (the delta kernel excluded).  NULL to skip.
+   * ev_main_mid is recorded between the dK/dV kernel and the dQ kernel: besides timing, another
+   * stream may wait for it (rswa_event_wait) and pick the K/V gradients up while dQ is computed;
+   * a ring rank sends the received spans' gradients back that way. */
   void* ev_main_start;
   void* ev_main_stop;
-  void* ev_main_mid; /* optional: recorded between the dK/dV kernel and the dQ kernel */
+  void* ev_main_mid;
 } rswa_bwd_params_t;
 
 int64_t rswa_bwd_workspace_bytes(int32_t batch, int32_t q_len, int32_t n_q_heads, int32_t head_dim);
@@ -254,12 +256,14 @@ int rswa_flag_wait(const int32_t* flag, int32_t value, int32_t* status, int64_t 
 int rswa_selftest_mma(int32_t mode, const void* a, const void* b, float* d, int32_t* status,
                       void* stream);
 
-/* Timing events for benchmarks (thin wrappers of cudaEvent_t so that callers need no CUDA headers).
- * No counterpart in the reference, which times with torch.cuda.Event
+/* Events (thin wrappers of cudaEvent_t so that callers need no CUDA headers): timing for benchmarks,
+ * and ordering between streams.  No counterpart in the reference, which times with torch.cuda.Event
  * (test/test_ring_swa_nonvarlen.py:295-320). */
 void* rswa_event_create(void);
 void rswa_event_destroy(void* ev);
 int rswa_event_record(void* ev, void* stream);
+/* work queued on `stream` after this call starts once the event's latest record has completed */
+int rswa_event_wait(void* ev, void* stream);
 /* milliseconds between two recorded events, after synchronising on `stop`; negative on error */
 float rswa_event_elapsed_ms(void* start, void* stop);
 

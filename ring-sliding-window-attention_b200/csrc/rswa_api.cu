@@ -417,6 +417,13 @@ extern "C" int rswa_event_record(void* ev, void* stream) {
   }
   return RSWA_OK;
 }
+extern "C" int rswa_event_wait(void* ev, void* stream) {
+  if (!ev || cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(ev), 0) != cudaSuccess) {
+    set_error("rswa_event_wait failed");
+    return RSWA_E_CUDA;
+  }
+  return RSWA_OK;
+}
 extern "C" float rswa_event_elapsed_ms(void* start, void* stop) {
   float ms = -1.f;
   if (!start || !stop) return -1.f;

@@ -112,6 +112,7 @@ SYMBOLS = {
     "rswa_event_create": (C.c_void_p, []),
     "rswa_event_destroy": (None, [C.c_void_p]),
     "rswa_event_record": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "rswa_event_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
     "rswa_event_elapsed_ms": (C.c_float, [C.c_void_p, C.c_void_p]),
     "rswa_selftest_mma": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }

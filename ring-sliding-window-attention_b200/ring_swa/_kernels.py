@@ -41,6 +41,7 @@ launch_count = 0
 bwd_main_events = None
 # Same for the forward kernel (one launch per rswa_fwd call).
 fwd_events = None
+_mid_event = {}   # per device: the event a one-call ring backward records between its two kernels
 
 
 def _dev_key(device: torch.device):
@@ -245,10 +246,12 @@ def bwd_workspace(q: torch.Tensor) -> torch.Tensor:
 def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor,
         dq: torch.Tensor, window: int, n_sink: int, scale: float, q_pos_start: int = 0,
         cu_seqlens: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
-        flags: int = _C.BWD_INIT | _C.BWD_FINISH) -> torch.Tensor:
+        flags: int = _C.BWD_INIT | _C.BWD_FINISH, mid_event: Optional[int] = None) -> torch.Tensor:
     """K/V gradients of the spans that carry dk/dv buffers, and (with BWD_FINISH) dq summed over ALL given
     spans.  A ring rank calls it twice: the received spans first (INIT; their gradients leave early), then
-    every span again with gradient buffers on the local one only (FINISH).  Returns the workspace."""
+    every span again with gradient buffers on the local one only (FINISH) -- or once with `mid_event`
+    (from mid_event_for): the call records that event between the dK/dV kernel and the dQ kernel, so that
+    another stream can pick the K/V gradients up while dQ is computed.  Returns the workspace."""
     for name, t in (("q", q), ("out", out), ("dout", dout), ("dq", dq)):
         _check4(name, t)
         if t.dtype != q.dtype or t.shape != q.shape:
@@ -273,14 +276,40 @@ def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.
     p.workspace_bytes = workspace.numel()
     p.flags = int(flags)
     p.status = status_word(q.device).data_ptr()
+    if mid_event is not None:
+        p.ev_main_mid = mid_event
     if bwd_main_events is not None:
-        p.ev_main_start, p.ev_main_mid, p.ev_main_stop = (_C.lib().rswa_event_create() for _ in range(3))
+        p.ev_main_start, p.ev_main_stop = (_C.lib().rswa_event_create() for _ in range(2))
+        if mid_event is None:
+            p.ev_main_mid = _C.lib().rswa_event_create()
         bwd_main_events.append((p.ev_main_start, p.ev_main_mid, p.ev_main_stop))
     _C.check(_C.lib().rswa_bwd(C.byref(p), _stream()), "rswa_bwd")
     global launch_count
     launch_count += ((1 if flags & _C.BWD_INIT else 0) + (1 if any(s.dk is not None for s in spans) else 0) +
                      (1 if flags & _C.BWD_FINISH else 0))
     return workspace
+
+
+def mid_event_for(device: torch.device) -> int:
+    """The event (raw handle) to hand to bwd(mid_event=...) on this device: one per device, recorded anew
+    by every call -- a stream that waits for it (stream_wait_event) right after the call sees that call's
+    record.  While benchmarks collect per-kernel times every call gets an event of its own, because
+    they read the times later."""
+    if bwd_main_events is not None:
+        return _C.lib().rswa_event_create()
+    key = _dev_key(device)
+    ev = _mid_event.get(key)
+    if ev is None:
+        with torch.cuda.device(device):
+            ev = _C.lib().rswa_event_create()
+        if not ev:
+            raise RuntimeError("rswa_event_create failed")
+        _mid_event[key] = ev
+    return ev
+
+
+def stream_wait_event(stream: torch.cuda.Stream, event: int) -> None:
+    _C.check(_C.lib().rswa_event_wait(C.c_void_p(event), C.c_void_p(stream.cuda_stream)), "rswa_event_wait")
 
 
 def bwd_noalloc(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.Tensor,

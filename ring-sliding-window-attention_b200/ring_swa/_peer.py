@@ -91,15 +91,19 @@ class PeerLink:
         return self.buf[off:off + nb].view(dtype).view(shape)
 
     # -- protocol
-    def put(self, direction: int, hop: int, dst: int, parts: List[torch.Tensor], ready: torch.cuda.Event) -> None:
+    def put(self, direction: int, hop: int, dst: int, parts: List[torch.Tensor], ready) -> None:
         """Move `parts` (tensors whose rows per leading index are contiguous; laid out one after the other
-        in the slot) into dst's slot for (direction, hop), on the side stream, behind `ready`."""
+        in the slot) into dst's slot for (direction, hop), on the side stream, behind `ready` (a
+        torch.cuda.Event, or the raw handle of an event of the kernel library)."""
         key = (direction, hop)
         n = self.sent.get(key, 0) + 1
         self.sent[key] = n
         data_base, ack_base = (_DATA_F, _ACK_F) if direction == 0 else (_DATA_B, _ACK_B)
         with torch.cuda.stream(self.side):
-            self.side.wait_event(ready)
+            if isinstance(ready, int):
+                K.stream_wait_event(self.side, ready)
+            else:
+                self.side.wait_event(ready)
             if n > 1:   # the receiver has read message n - 1 out of the slot
                 K.flag_wait(self.flag_ptr(self.rank, ack_base, hop), n - 1, self.device, WAIT_TIMEOUT_S)
             base = self.slot_ptr(dst, direction, hop)

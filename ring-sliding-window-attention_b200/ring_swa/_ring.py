@@ -282,7 +282,12 @@ class RingAttn(torch.autograd.Function):
         ws = K.bwd_workspace(q4)
         link = ctx.link
         ops, recvs = [], []   # recvs: (offset, tokens, gradient tensor, (hop, sender) when it sits in a peer slot)
-        if remote:
+        # With peer stores (a copy-engine put behind an event, no message that the host must post between
+        # two calls) the whole backward is ONE call: dK/dV of the received and the local spans in one launch,
+        # the received spans' gradients picked up by the side stream while dQ is computed.  Sink gradients
+        # travel as messages and many ranks wait for them: with a remote sink the two-call form stays.
+        one_call = link is not None and bool(remote) and not sink_remote
+        if remote and not one_call:
             with _phase("bwd.halo_spans"):
                 K.bwd(q4, remote, out, lse, do4, dq4, workspace=ws, flags=_C.BWD_INIT, **args)
             if link is not None:
@@ -329,10 +334,18 @@ class RingAttn(torch.autograd.Function):
             local = [K.KVSpan(k4, v4, plan.q_pos_start, dk=dk4, dv=dv4)]
         # second call: dK/dV of the local span, and dQ over every span (the received ones without
         # gradient buffers, their gradients are already on the wire)
-        seen = [K.KVSpan(s.k, s.v, s.pos_start) for s in remote]
-        flags = _C.BWD_FINISH | (0 if remote else _C.BWD_INIT)
-        with _phase("bwd.local_and_dq"):
-            K.bwd(q4, seen + local, out, lse, do4, dq4, workspace=ws, flags=flags, **args)
+        if one_call:
+            mid = K.mid_event_for(q4.device)
+            with _phase("bwd.local_and_dq"):
+                K.bwd(q4, remote + local, out, lse, do4, dq4, workspace=ws, flags=_C.BWD_INIT | _C.BWD_FINISH,
+                      mid_event=mid, **args)
+            for r, g in zip(plan.halo_recv, remote_grads):
+                link.put(1, r.hop, r.src, [g], mid)
+        else:
+            seen = [K.KVSpan(s.k, s.v, s.pos_start) for s in remote]
+            flags = _C.BWD_FINISH | (0 if remote else _C.BWD_INIT)
+            with _phase("bwd.local_and_dq"):
+                K.bwd(q4, seen + local, out, lse, do4, dq4, workspace=ws, flags=flags, **args)
         with _phase("bwd.grad_wait"):
             _wait(works)
         if acc is not None:
