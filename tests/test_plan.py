@@ -183,3 +183,14 @@ def test_rejects_bad_geometry():
         make_plan(4, 4, 16, 5, 0, None)
     with pytest.raises(ValueError):
         make_plan(2, 0, 0, 5, 0, None)
+
+
+def test_chunk_lens_must_add_up_to_the_packed_axis():
+    """cp_chunk_lens is checked where the reference checks its equal share (before any work is queued)."""
+    import torch
+    import ring_swa
+    q = torch.zeros(6, 2, 8)
+    cu = torch.tensor([0, 4, 10], dtype=torch.int32)
+    for fn in (ring_swa.ring_sliding_window_attn_varlen, ring_swa.ring_streaming_llm_attn_varlen):
+        with pytest.raises(AssertionError, match="cp_chunk_lens does not add up"):
+            fn(q, q, q, 3, cu, cp_size=2, cp_chunk_lens=[6, 5])
