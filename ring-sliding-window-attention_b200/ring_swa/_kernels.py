@@ -41,7 +41,7 @@ launch_count = 0
 bwd_main_events = None
 # Same for the forward kernel (one launch per rswa_fwd call).
 fwd_events = None
-_mid_event = {}   # per device: the event a one-call ring backward records between its two kernels
+_mid_event = {}   # per (device, stream): the event a one-call ring backward records between its two kernels
 
 
 def _dev_key(device: torch.device):
@@ -291,13 +291,14 @@ def bwd(q: torch.Tensor, spans: Sequence[KVSpan], out: torch.Tensor, lse: torch.
 
 
 def mid_event_for(device: torch.device) -> int:
-    """The event (raw handle) to hand to bwd(mid_event=...) on this device: one per device, recorded anew
-    by every call -- a stream that waits for it (stream_wait_event) right after the call sees that call's
-    record.  While benchmarks collect per-kernel times every call gets an event of its own, because
-    they read the times later."""
+    """The event (raw handle) to hand to bwd(mid_event=...) on this device's current stream: one per
+    (device, stream), recorded anew by every call -- a stream that waits for it (stream_wait_event) right
+    after the call sees that call's record or a later one of the same stream, behind which the call's
+    dK/dV kernel has finished either way.  While benchmarks collect per-kernel times every call gets an
+    event of its own, because they read the times later."""
     if bwd_main_events is not None:
         return _C.lib().rswa_event_create()
-    key = _dev_key(device)
+    key = _dev_key(device) + (_stream().value,)
     ev = _mid_event.get(key)
     if ev is None:
         with torch.cuda.device(device):
