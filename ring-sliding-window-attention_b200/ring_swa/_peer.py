@@ -134,20 +134,27 @@ class PeerLink:
 _links: Dict[Tuple, PeerLink] = {}
 
 
+def slot_bytes_for(cp: int, S: int, W: int, batch: int, hkv: int, head_dim: int,
+                   S_min: Optional[int] = None) -> Optional[List[int]]:
+    """Bytes of the receive slot of every hop (float32 gradients included) for a geometry, or None when
+    nothing travels or the window reaches over more chunks than there are flag words for.  `S` is the
+    largest chunk of the group and `S_min` the smallest where they differ: a message holds at most S
+    tokens, and the window reaches over at most ceil(W / S_min) chunks."""
+    S_min = S if S_min is None else S_min
+    hops = min((W + S_min - 1) // S_min, cp - 1)
+    if hops < 1 or hops > MAX_HOPS:
+        return None
+    return [2 * batch * min(S, max(0, W - (h - 1) * S_min)) * hkv * head_dim * 4 for h in range(1, hops + 1)]
+
+
 def link_for(group, device: torch.device, cp: int, S: int, W: int, batch: int, hkv: int, head_dim: int,
              S_min: Optional[int] = None) -> Optional[PeerLink]:
     """The link of this (group, device), its slots large enough for every halo message of the geometry
-    (float32 gradients included).  Every rank of the group must call this with the same arguments, the
-    first time and whenever a larger geometry shows up (a collective set-up).  `S` is the largest chunk of
-    the group and `S_min` the smallest where they differ: a message holds at most S tokens, and the window
-    reaches over at most ceil(W / S_min) chunks."""
-    S_min = S if S_min is None else S_min
-    hops = min((W + S_min - 1) // S_min, cp - 1)
-    if hops < 1:
+    (slot_bytes_for).  Every rank of the group must call this with the same arguments, the first time and
+    whenever a larger geometry shows up (a collective set-up)."""
+    need = slot_bytes_for(cp, S, W, batch, hkv, head_dim, S_min)
+    if need is None:
         return None
-    if hops > MAX_HOPS:
-        return None
-    need = [2 * batch * min(S, max(0, W - (h - 1) * S_min)) * hkv * head_dim * 4 for h in range(1, hops + 1)]
     key = (id(group), device.index)
     link = _links.get(key)
     if link is not None and len(link.slot_bytes) >= len(need) and all(a >= b for a, b in zip(link.slot_bytes, need)):

@@ -194,3 +194,33 @@ def test_chunk_lens_must_add_up_to_the_packed_axis():
     for fn in (ring_swa.ring_sliding_window_attn_varlen, ring_swa.ring_streaming_llm_attn_varlen):
         with pytest.raises(AssertionError, match="cp_chunk_lens does not add up"):
             fn(q, q, q, 3, cu, cp_size=2, cp_chunk_lens=[6, 5])
+
+
+def test_peer_slots_hold_every_halo_message():
+    """The receive slots of the peer-store exchange are sized from the largest and the smallest chunk only
+    (every rank must come to the same layout): no halo message of any rank's plan may be larger than the
+    slot of its hop, forward (16-bit K/V) or backward (gradients, float32 at most), and no plan may need a
+    hop without a slot."""
+    import random
+    from ring_swa._peer import MAX_HOPS, slot_bytes_for
+    rng = random.Random(5)
+    B, hkv, D = 2, 3, 128
+    for trial in range(2000):
+        cp = rng.randint(2, 6)
+        if rng.random() < 0.4:
+            lens = [rng.choice([1, 2, 5, 8, 16])] * cp
+        else:
+            lens = [rng.choice([1, 2, 3, 5, 8, 13, 16]) for _ in range(cp)]
+        W = rng.randint(0, sum(lens) + 2)
+        cuts = sorted(rng.sample(range(1, sum(lens)), rng.randint(0, 3))) if sum(lens) > 3 else []
+        cu = [0] + cuts + [sum(lens)]
+        slots = slot_bytes_for(cp, max(lens), W, B, hkv, D, min(lens))
+        plans = [make_plan(cp, r, lens[r], W, 0, cu, lens) for r in range(cp)]
+        top = max([h.hop for p in plans for h in p.halo_recv], default=0)
+        if slots is None:
+            assert top == 0 or (W + min(lens) - 1) // min(lens) > MAX_HOPS
+            continue
+        assert top <= len(slots), (lens, W, cu)
+        for p in plans:
+            for h in p.halo_recv:
+                assert 2 * B * h.length * hkv * D * 4 <= slots[h.hop - 1], (lens, W, cu, h)
