@@ -37,3 +37,16 @@ def ring_sliding_window_attn(
     _check_nonvarlen(q, k, v)
     ring = ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank)
     return attention(q, k, v, window_size, 0, softmax_scale, None, None, ring)
+
+
+class RingSlidingWindowAttn:
+    """The reference's autograd class by name (ring_swa/sliding_window/nonvarlen.py:17-32): `apply` takes
+    its forward's positional arguments in its order.  `cp_stream` is accepted and not used (the halo
+    exchange runs on a stream of its own); differentiation goes through the one autograd function
+    behind ring_sliding_window_attn."""
+
+    @staticmethod
+    def apply(q, k, v, window_size, cp_group, cp_size, cp_local_rank, cp_prev_global_rank,
+              cp_next_global_rank, cp_stream=None, softmax_scale=None):
+        return ring_sliding_window_attn(q, k, v, window_size, cp_group, cp_size, cp_local_rank,
+                                        cp_prev_global_rank, cp_next_global_rank, softmax_scale)

@@ -81,3 +81,15 @@ def ring_sliding_window_attn_varlen(
     cu_seqlens, cu_host = _varlen_prologue(q, k, v, cu_seqlens, cp_size, cp_chunk_lens)
     ring = ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank, cp_chunk_lens)
     return attention(q, k, v, window_size, 0, softmax_scale, cu_seqlens, cu_host, ring)
+
+
+class RingSlidingWindowAttnVarlen:
+    """The reference's autograd class by name (ring_swa/sliding_window/varlen.py:19-36): `apply` takes
+    its forward's positional arguments in its order; `max_seqlen` and `cp_stream` are accepted and
+    not used."""
+
+    @staticmethod
+    def apply(q, k, v, window_size, cu_seqlens, max_seqlen, cp_group, cp_size, cp_local_rank,
+              cp_prev_global_rank, cp_next_global_rank, cp_stream=None, softmax_scale=None):
+        return ring_sliding_window_attn_varlen(q, k, v, window_size, cu_seqlens, cp_group, cp_size, cp_local_rank,
+                                               cp_prev_global_rank, cp_next_global_rank, softmax_scale)

@@ -19,3 +19,20 @@ def naive_streaming_llm_attn_varlen(q, k, v, window_size: int, cu_seqlens: torch
                                     softmax_scale: Optional[float] = None):
     return ring_streaming_llm_attn_varlen(q, k, v, window_size, cu_seqlens, cp_size=1,
                                           softmax_scale=softmax_scale)
+
+
+class StreamingLLMAttn:
+    """The reference's single-GPU autograd class by name (ring_swa/streaming_llm/naive.py:11-20):
+    apply(q, k, v, window_size, softmax_scale)."""
+
+    @staticmethod
+    def apply(q, k, v, window_size, softmax_scale=None):
+        return naive_streaming_llm_attn(q, k, v, window_size, softmax_scale)
+
+
+class StreamingLLMAttnVarlen:
+    """ring_swa/streaming_llm/naive.py:90-100: apply(q, k, v, window_size, cu_seqlens, softmax_scale)."""
+
+    @staticmethod
+    def apply(q, k, v, window_size, cu_seqlens, softmax_scale=None):
+        return naive_streaming_llm_attn_varlen(q, k, v, window_size, cu_seqlens, softmax_scale)

@@ -33,3 +33,14 @@ def ring_streaming_llm_attn(
     _check_nonvarlen(q, k, v)
     ring = ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank)
     return attention(q, k, v, window_size, num_sink_tokens, softmax_scale, None, None, ring)
+
+
+class RingStreamingLLMAttn:
+    """The reference's autograd class by name (ring_swa/streaming_llm/nonvarlen.py:20-35): `apply` takes
+    its forward's positional arguments in its order (one sink token); `cp_stream` is accepted and not used."""
+
+    @staticmethod
+    def apply(q, k, v, window_size, cp_group, cp_size, cp_local_rank, cp_prev_global_rank,
+              cp_next_global_rank, cp_stream=None, softmax_scale=None):
+        return ring_streaming_llm_attn(q, k, v, window_size, cp_group, cp_size, cp_local_rank,
+                                       cp_prev_global_rank, cp_next_global_rank, softmax_scale)

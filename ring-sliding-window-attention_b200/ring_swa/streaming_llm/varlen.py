@@ -36,3 +36,15 @@ def ring_streaming_llm_attn_varlen(
     cu_seqlens, cu_host = _varlen_prologue(q, k, v, cu_seqlens, cp_size, cp_chunk_lens)
     ring = ring_ctx(cp_group, cp_size, cp_local_rank, cp_prev_global_rank, cp_next_global_rank, cp_chunk_lens)
     return attention(q, k, v, window_size, num_sink_tokens, softmax_scale, cu_seqlens, cu_host, ring)
+
+
+class RingStreamingLLMVarlen:
+    """The reference's autograd class by name (ring_swa/streaming_llm/varlen.py:20-37): `apply` takes its
+    forward's positional arguments in its order (one sink token); `max_seqlen` and `cp_stream` are
+    accepted and not used."""
+
+    @staticmethod
+    def apply(q, k, v, window_size, cu_seqlens, max_seqlen, cp_group, cp_size, cp_local_rank,
+              cp_prev_global_rank, cp_next_global_rank, cp_stream=None, softmax_scale=None):
+        return ring_streaming_llm_attn_varlen(q, k, v, window_size, cu_seqlens, cp_group, cp_size, cp_local_rank,
+                                              cp_prev_global_rank, cp_next_global_rank, softmax_scale)

@@ -88,7 +88,16 @@ def run_rank(rank, ws, port, jobs, outdir, device="cpu"):
             kw["cp_chunk_lens"] = job["chunk_lens"]
         if job.get("n_sink", 1) != 1 and "streaming" in job["fn"]:
             kw["num_sink_tokens"] = job["n_sink"]
-        out = fn(ql, kl, vl, **kw)
+        if job.get("cls"):
+            # through the reference's autograd class name: positional arguments in the reference's order
+            import importlib
+            mod, name = job["cls"].split(":")
+            cls = getattr(importlib.import_module("ring_swa." + mod), name)
+            pos = [ql, kl, vl, job["W"]] + ([kw["cu_seqlens"], None] if varlen else [])
+            pos += [dist.group.WORLD, ws, rank, (rank - 1) % ws, (rank + 1) % ws, None, None]
+            out = cls.apply(*pos)
+        else:
+            out = fn(ql, kl, vl, **kw)
         out.backward(dol)
         errs = {}
         for name, got in (("out", out.detach()), ("dq", ql.grad), ("dk", kl.grad), ("dv", vl.grad)):

@@ -61,6 +61,18 @@ def test_varlen_functions():
         out, dq, dk, dv = _run(fn, q, k, v, do, window_size=90, cu_seqlens=cud, cp_size=1, softmax_scale=0.1)
         for n, a, b in (("out", out, ro[0]), ("dq", dq, rdq[0]), ("dk", dk, rdk[0]), ("dv", dv, rdv[0])):
             assert_close(n, a, b)
+    # the single-GPU names of ring_swa/streaming_llm/naive.py (function :232 and class :90) and the ring
+    # classes' apply() with the reference's positional arguments give the same tensors
+    from ring_swa.sliding_window.varlen import RingSlidingWindowAttnVarlen
+    from ring_swa.streaming_llm.naive import StreamingLLMAttnVarlen, naive_streaming_llm_attn_varlen
+    slm, *_ = _run(ring_swa.ring_streaming_llm_attn_varlen, q, k, v, do, window_size=90, cu_seqlens=cud, cp_size=1, softmax_scale=0.1)
+    a1, *_ = _run(naive_streaming_llm_attn_varlen, q, k, v, do, window_size=90, cu_seqlens=cud, softmax_scale=0.1)
+    a2, *_ = _run(lambda q_, k_, v_: StreamingLLMAttnVarlen.apply(q_, k_, v_, 90, cud, 0.1), q, k, v, do)
+    assert torch.equal(slm, a1) and torch.equal(slm, a2)
+    swa, *_ = _run(ring_swa.ring_sliding_window_attn_varlen, q, k, v, do, window_size=90, cu_seqlens=cud, cp_size=1, softmax_scale=0.1)
+    a3, *_ = _run(lambda q_, k_, v_: RingSlidingWindowAttnVarlen.apply(q_, k_, v_, 90, cud, None, None, 1, 0, None, None, None, 0.1),
+                  q, k, v, do)
+    assert torch.equal(swa, a3)
 
 
 def test_device_side_timeout_reaches_the_host_and_clears():

@@ -116,3 +116,20 @@ def test_chunks_of_different_lengths_cp3():
     ]
     res = _spawn(3, 29761, jobs)
     _assert_small(res, jobs, TOL)
+
+
+@pytest.mark.timeout(600)
+def test_reference_class_names_cp2():
+    """RingSlidingWindowAttn.apply(...) and its three siblings take the reference's positional arguments
+    (ring_swa/sliding_window/nonvarlen.py:17-32, varlen.py:19-36, streaming_llm/nonvarlen.py:20-35,
+    varlen.py:20-37) and give the ring functions' results."""
+    jobs = [
+        dict(_dense_job("ring_sliding_window_attn", 600, 1, 2, 1, 8, 100, 51), cls="sliding_window.nonvarlen:RingSlidingWindowAttn"),
+        dict(_dense_job("ring_sliding_window_attn_varlen", 600, None, 2, 1, 8, 70, 52, cu=[0, 300, 301, 420, 600]),
+             cls="sliding_window.varlen:RingSlidingWindowAttnVarlen"),
+        dict(_dense_job("ring_streaming_llm_attn", 600, 1, 2, 1, 8, 60, 53, n_sink=1), cls="streaming_llm.nonvarlen:RingStreamingLLMAttn"),
+        dict(_dense_job("ring_streaming_llm_attn_varlen", 600, None, 2, 1, 8, 50, 54, cu=[0, 130, 500, 600], n_sink=1),
+             cls="streaming_llm.varlen:RingStreamingLLMVarlen"),
+    ]
+    res = _spawn(2, 29781, jobs)
+    _assert_small(res, jobs, TOL)
