@@ -32,3 +32,9 @@ def merge_attn_out(attn_out: torch.Tensor, softmax_lse: torch.Tensor, new_attn_o
         if new_softmax_lse.stride() != softmax_lse.stride():
             raise ValueError("merge_attn_out: the two lse tensors must share their layout")
     K.merge(attn_out, softmax_lse, new_attn_out, new_softmax_lse)
+
+
+# The reference binds merge_attn_out to its Triton kernel wrapper of this name where Triton >= 3 is present
+# (ring_swa/ops/merge.py:150, 196-200); code that imports that name gets the CUDA kernels here.  Its pure
+# torch variant (torch_merge_attn_out, :16-66) has no counterpart: there is no path without the library.
+triton_merge_attn_out = merge_attn_out
