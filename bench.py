@@ -184,6 +184,28 @@ def cpu_tokens_per_s(seconds, sample, wl):
     return sample["S"] * (sample["H"] / wl["Hq"]) / seconds
 
 
+def cpu_small_config():
+    """The smallest configuration of the benchmark set (fp32, 1 x 1024 tokens, 4/4 heads of 64, window 128,
+    scale 1/8, seed 0) is the one the reference's own CPU-runnable code path covers: its dense torch
+    formulation (test/test_local_swa.py:7-95, restated in oracle/), forward + backward, after 2 warm-up
+    calls, median of 10.  It executes dense S^2 work; the in-window figure counts 14*D*Hq*pairs."""
+    from oracle.dense_attn import dense_attn_fwd_bwd
+    S, H, d, W = 1024, 4, 64, 128
+    g = torch.Generator().manual_seed(0)
+    q, k, v, do = (torch.randn(1, S, H, d, generator=g) for _ in range(4))
+    ts = []
+    for i in range(12):
+        t0 = time.perf_counter()
+        dense_attn_fwd_bwd(q, k, v, do, W, 0.125, 0)
+        ts.append(time.perf_counter() - t0)
+    sec = statistics.median(ts[2:])
+    pairs = W * (W + 1) // 2 + (S - W) * (W + 1)
+    return {"workload": f"fp32 B=1 S={S} Hq=Hkv={H} D={d} window={W} fwd+bwd, dense torch on the host",
+            "ms": 1e3 * sec, "tokens_per_s": S / sec, "in_window_gflops": 14 * d * H * pairs / sec / 1e9,
+            "executed_dense_gflops": 14 * d * H * (S * S) / sec / 1e9,
+            "threads": torch.get_num_threads(), "cpu_count": os.cpu_count()}
+
+
 def use_host_cores():
     """torch.distributed.run starts its workers with OMP_NUM_THREADS=1; the CPU arm is meant to use
     the host's cores, so give torch as many threads as a plain start takes (one per physical core)."""
@@ -217,6 +239,7 @@ def run_reference(args, wl):
                          "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "cpu_small_config": cpu_small_config(),
     }
     print(json.dumps(line), flush=True)
 
@@ -726,6 +749,10 @@ def main():
                 "cores": torch.get_num_threads(), "kind": "port",
                 "sample": f"{len(runs)} dense fp32 fwd+bwd passes over a 1 x {CPU_SAMPLE['S']} x {CPU_SAMPLE['H']}-head "
                           f"slice (of {Hq} heads), median; tokens scaled by the head fraction"}
+            try:
+                line["cpu_small_config"] = cpu_small_config()
+            except Exception as e:                          # noqa: BLE001  (an extra figure must not cost the line)
+                line["cpu_small_config"] = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
         print(json.dumps(line), flush=True)
     if n > 1:
         dist.barrier()
